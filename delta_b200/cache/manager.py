@@ -44,6 +44,7 @@ class LayerCacheView:
     writes: bool
     window: Optional[int]
     group: str
+    state: Optional[dict] = None    # per-run state tensors of a mixer that declares some beside its pages
 
 
 class CacheGroup:

@@ -36,8 +36,10 @@ def unregister_architecture(name: str) -> None:
 
 def architecture_of(config_json: dict) -> Architecture:
     archs = config_json.get("architectures") or []
+    if not archs and isinstance(config_json.get("architecture"), str):
+        archs = [config_json["architecture"]]      # some designs name themselves in the singular
     if not archs:
-        raise ConfigError("config.json has no 'architectures'")
+        raise ConfigError("config.json has no 'architectures' (nor 'architecture')")
     name = archs[0]
     if name not in ARCHITECTURES:
         raise ConfigError(f"unknown architecture '{name}'; known: {', '.join(sorted(ARCHITECTURES))}")

@@ -10,7 +10,11 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) gemm_nt_kernel(const TI* __restrict__ A, const TI* __restrict__ W, TO* __restrict__ C,
-                                                      int M, int N, int K, int lda, int ldw, int ldc) {
+                                                      int M, int N, int K, int lda, int ldw, int ldc,
+                                                      long long sa, long long sw, long long sc) {
+  A += (size_t)blockIdx.z * sa;      // one product per blockIdx.z: the operands of the next lie sa, sw, sc elements on
+  W += (size_t)blockIdx.z * sw;
+  C += (size_t)blockIdx.z * sc;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -74,11 +78,31 @@ extern "C" int dk_gemm_nt_plain(const void* A, const void* W, void* C, int M, in
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   DK_REQUIRE(grid.y <= 65535, "gemm: M=%d is too large for this kernel", M);
 #define LAUNCH(TI, TO) \
-  gemm_nt_kernel<TI, TO><<<grid, 256, 0, stream>>>((const TI*)A, (const TI*)W, (TO*)C, M, N, K, lda, ldw, ldc)
+  gemm_nt_kernel<TI, TO><<<grid, 256, 0, stream>>>((const TI*)A, (const TI*)W, (TO*)C, M, N, K, lda, ldw, ldc, 0, 0, 0)
   if (in_dtype == DK_F32 && out_dtype == DK_F32) LAUNCH(float, float);
   else if (in_dtype == DK_BF16 && out_dtype == DK_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (in_dtype == DK_BF16 && out_dtype == DK_F32) LAUNCH(__nv_bfloat16, float);
   else DK_REQUIRE(false, "gemm: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
 #undef LAUNCH
   return dk_check_launch("gemm_nt_plain");
+}
+
+// `batch` products of the same sizes in one launch (one per head of an attention layer, say): product b reads
+// A + b*sa, W + b*sw and writes C + b*sc (strides in elements; the operands may interleave, as heads do in a row).
+extern "C" int dk_gemm_nt_plain_batched(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
+                                        int batch, long long sa, long long sw, long long sc, int in_dtype, int out_dtype,
+                                        cudaStream_t stream) {
+  if (M == 0 || N == 0 || batch == 0) return 0;
+  DK_REQUIRE(M > 0 && N > 0 && K > 0 && batch > 0, "gemm: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
+  DK_REQUIRE(batch <= 65535, "gemm: %d products in one launch are too many", batch);
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+  DK_REQUIRE(grid.y <= 65535, "gemm: M=%d is too large for this kernel", M);
+#define LAUNCH(TI, TO) \
+  gemm_nt_kernel<TI, TO><<<grid, 256, 0, stream>>>((const TI*)A, (const TI*)W, (TO*)C, M, N, K, lda, ldw, ldc, sa, sw, sc)
+  if (in_dtype == DK_F32 && out_dtype == DK_F32) LAUNCH(float, float);
+  else if (in_dtype == DK_BF16 && out_dtype == DK_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == DK_BF16 && out_dtype == DK_F32) LAUNCH(__nv_bfloat16, float);
+  else DK_REQUIRE(false, "gemm: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+#undef LAUNCH
+  return dk_check_launch("gemm_nt_plain_batched");
 }

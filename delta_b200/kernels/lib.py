@@ -36,7 +36,30 @@ class AttnParams(C.Structure):
     ]
 
 
+class RowAttnParams(C.Structure):
+    """Mirror of ``DkRowAttnParams`` in csrc/row_attention_params.h."""
+    _fields_ = [
+        ("q", P), ("out", P), ("cache", P), ("block_table", P), ("tok_row", P), ("tok_pos", P), ("row_q_start", P),
+        ("row_q_len", P), ("row_pos_start", P), ("sink", P), ("scratch", P), ("err", P),
+        ("T", I), ("rows", I), ("H", I), ("KV", I), ("dk", I), ("dv", I), ("ps", I), ("max_pages", I), ("num_pages", I),
+        ("q_stride", I), ("q_head_stride", I), ("row_width", I), ("k_off", I), ("v_off", I), ("window", I), ("dtype", I),
+        ("splits", I), ("row_filter", I), ("scale", F), ("reserved", I),
+    ]
+
+
+L = C.c_longlong
+
 _SIGNATURES = {
+    "dk_embedding_streams": [P, P, P, I, I, I, I, I, P, P],
+    "dk_stream_norm": [P, P, P, P, P, P, P, P, I, I, I, F, I, I, I, P],
+    "dk_activation": [P, P, L, I, I, P],
+    "dk_softcap": [P, L, F, P],
+    "dk_conv_silu": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "dk_selective_scan": [P, P, P, I, I, I, P, I, P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "dk_attention_rows_plain": [C.POINTER(RowAttnParams), P],
+    "dk_rows_append": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
+    "dk_latent_prepare": [P, I, P, P, P, I, P, I, P, I, I, I, P, F, P, I, I, I, I, I, I, I, P, P],
+    "dk_gemm_nt_plain_batched": [P, P, P, I, I, I, I, I, I, I, L, L, L, I, I, P],
     "dk_embedding": [P, P, P, I, I, I, I, P, P],
     "dk_rms_norm": [P, P, P, P, P, I, I, F, I, I, I, P],
     "dk_silu_mul": [P, P, I, I, I, P],
@@ -83,6 +106,10 @@ def load():
         lib.dk_attention_decode_scratch_floats.argtypes = [I, I, I, I]
         lib.dk_gemm_stream_k_workspace_bytes.restype = C.c_longlong
         lib.dk_gemm_stream_k_workspace_bytes.argtypes = [I]
+        lib.dk_sizeof_row_attn_params.restype = I
+        if lib.dk_sizeof_row_attn_params() != C.sizeof(RowAttnParams):
+            raise KernelError(f"RowAttnParams is {C.sizeof(RowAttnParams)} bytes in Python and "
+                              f"{lib.dk_sizeof_row_attn_params()} in the library: the two declarations differ")
         if lib.dk_sizeof_attn_params() != C.sizeof(AttnParams):
             raise KernelError(f"AttnParams is {C.sizeof(AttnParams)} bytes in Python and "
                               f"{lib.dk_sizeof_attn_params()} in the library: the two declarations differ")

@@ -404,3 +404,174 @@ def sample(logits, out, temperature=None, top_p=None, seeds=None, positions=None
                                  _ptr(seeds, "seeds", torch.int64), _ptr(positions, "positions", torch.int32),
                                  _ptr(out, "out", torch.int32), _ptr(err, "err", torch.int32), _stream()), "sample")
     return out
+
+
+# ---- a residual stream in 32 bit, one copy or several mixed ones ------------------------------------------
+
+def embedding_streams(tokens, table, X, err=None):
+    """X[t, s, :] = table[tokens[t]] for every copy s; X is float32 [T, S, d]."""
+    T, S, d = X.shape
+    _l.check(_l.load().dk_embedding_streams(_ptr(tokens, "tokens", torch.int32), _ptr(table, "table"), _ptr(X, "X", torch.float32),
+                                            T, S, d, table.shape[0], dtype_code(table.dtype), _ptr(err, "err", torch.int32), _stream()),
+             "embedding_streams")
+    return X
+
+
+def stream_norm(X, out, *, weight=None, eps=0.0, read=None, update=None, rows=None, write_back=True):
+    """The step between two sublayers on a stream X [T, S, d] (float32).  ``update`` = (y, mix, out_w): the
+    copies first become  X_t <- sum_s mix[s, t] X_s + out_w[t] y  (stored when ``write_back``); then
+    u = sum_s read[s] X_s (``read`` None: the plain sum) and ``out`` = rmsnorm(u) * weight (``weight`` None: u
+    itself).  ``rows``: only these tokens, in this order.  ``out`` None: only the update is done."""
+    T, S, d = X.shape
+    n = (rows.shape[0] if rows is not None else T)
+    y = mix = out_w = None
+    if update is not None:
+        y, mix, out_w = update
+        if tuple(y.shape) != (T, d):
+            raise KernelError(f"stream_norm: the update has shape {tuple(y.shape)}, the stream rows {(T, d)}")
+    if out is not None and tuple(out.shape) != (n, d):
+        raise KernelError(f"stream_norm: the output has shape {tuple(out.shape)}, expected {(n, d)}")
+    f32 = torch.float32
+    _l.check(_l.load().dk_stream_norm(
+        _ptr(X, "X", f32), _ptr(y, "y"), _ptr(mix, "mix", f32), _ptr(out_w, "out_w", f32), _ptr(read, "read", f32),
+        _ptr(weight, "weight", f32), _ptr(out, "out"), _ptr(rows, "rows", torch.int32), n, S, d, float(eps),
+        int(bool(write_back)), dtype_code(y.dtype) if y is not None else (dtype_code(out.dtype) if out is not None else F32),
+        dtype_code(out.dtype) if out is not None else F32, _stream()), "stream_norm")
+    return out
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x, out, kind: str):
+    """Element by element: relu(x)^2, gelu in its tanh form, or silu."""
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"unknown activation '{kind}'; known: {', '.join(ACTIVATIONS)}")
+    _l.check(_l.load().dk_activation(_ptr(x, "x"), _ptr(out, "out", x.dtype), x.numel(), ACTIVATIONS[kind], dtype_code(x.dtype),
+                                     _stream()), "activation")
+    return out
+
+
+def softcap(logits, cap: float):
+    """logits <- cap * tanh(logits / cap), in place (float32)."""
+    _l.check(_l.load().dk_softcap(_ptr(logits, "logits", torch.float32), logits.numel(), float(cap), _stream()), "softcap")
+    return logits
+
+
+# ---- the selective state-space mixer ----------------------------------------------------------------------
+
+def conv_silu(xin, in_stride, weight, bias, conv_state, out, *, tok_row, row_slot, row_q_start, row_q_len):
+    """Causal convolution over each row's tokens and silu; ``xin`` holds a token's C inputs at the start of rows of
+    ``in_stride`` elements.  ``conv_state`` [slots, taps-1, C] (float32) supplies the inputs before the step's first
+    token and is left holding the last taps-1 inputs of every row."""
+    T, C_ = out.shape
+    taps = weight.shape[1]
+    i32, f32 = torch.int32, torch.float32
+    _l.check(_l.load().dk_conv_silu(
+        _ptr(xin, "xin", out.dtype), int(in_stride), _ptr(weight, "weight", f32), _ptr(bias, "bias", f32),
+        _ptr(conv_state, "conv_state", f32), _ptr(out, "out"), _ptr(tok_row, "tok_row", i32), _ptr(row_slot, "row_slot", i32),
+        _ptr(row_q_start, "row_q_start", i32), _ptr(row_q_len, "row_q_len", i32), T, row_slot.shape[0], C_, taps,
+        dtype_code(out.dtype), _stream()), "conv_silu", 2 if taps > 1 else 1)
+    return out
+
+
+def selective_scan(x, dtraw, bc, b_off, c_off, z, z_stride, A_log, D, dt_bias, scan_state, out, *, row_slot, row_q_start,
+                   row_q_len):
+    """The recurrence of the selective state-space mixer over each row's tokens, from and into ``scan_state``
+    [slots, C, N] (float32).  ``bc`` [T, stride] holds a token's input map at ``b_off`` and output map at ``c_off``
+    (N each); ``z`` points at the gate's C values in rows of ``z_stride`` elements."""
+    T, C_ = x.shape
+    N = A_log.shape[1]
+    i32, f32 = torch.int32, torch.float32
+    _l.check(_l.load().dk_selective_scan(
+        _ptr(x, "x"), _ptr(dtraw, "dtraw", x.dtype), _ptr(bc, "bc", x.dtype), bc.shape[1], int(b_off), int(c_off), z, int(z_stride),
+        _ptr(A_log, "A_log", f32), _ptr(D, "D", f32), _ptr(dt_bias, "dt_bias", f32), _ptr(scan_state, "scan_state", f32),
+        _ptr(out, "out", x.dtype), _ptr(row_slot, "row_slot", i32), _ptr(row_q_start, "row_q_start", i32),
+        _ptr(row_q_len, "row_q_len", i32), row_slot.shape[0], C_, N, dtype_code(x.dtype), _stream()), "selective_scan")
+    return out
+
+
+# ---- attention over a cache of rows -----------------------------------------------------------------------
+
+RowAttnParams = _l.RowAttnParams
+
+
+def row_attn_params(*, q, q_stride, q_head_stride, out, cache, block_table, tok_row, tok_pos, row_q_start, row_q_len,
+                    row_pos_start, H, KV, dk, dv, ps, row_width, k_off, v_off, scale, window=0, sink=None, err=None) -> RowAttnParams:
+    i32 = torch.int32
+    if tuple(cache.shape[1:]) != (KV, ps, row_width) or cache.dtype != q.dtype:
+        raise KernelError(f"attention_rows: cache has shape {tuple(cache.shape)} / {cache.dtype}, expected [pages, {KV}, {ps}, {row_width}] of {q.dtype}")
+    p = RowAttnParams()
+    p.q, p.out, p.cache = _ptr(q, "q"), _ptr(out, "out", q.dtype), _ptr(cache, "cache")
+    p.block_table = _ptr(block_table, "block_table", i32)
+    p.tok_row, p.tok_pos = _ptr(tok_row, "tok_row", i32), _ptr(tok_pos, "tok_pos", i32)
+    p.row_q_start, p.row_q_len = _ptr(row_q_start, "row_q_start", i32), _ptr(row_q_len, "row_q_len", i32)
+    p.row_pos_start = _ptr(row_pos_start, "row_pos_start", i32)
+    p.sink = _ptr(sink, "sink", torch.float32)
+    p.err = _ptr(err, "err", i32)
+    p.T, p.rows = tok_row.shape[0], block_table.shape[0]
+    p.H, p.KV, p.dk, p.dv, p.ps = H, KV, dk, dv, ps
+    p.max_pages, p.num_pages = block_table.shape[1], cache.shape[0]
+    p.q_stride, p.q_head_stride = int(q_stride), int(q_head_stride)
+    p.row_width, p.k_off, p.v_off = row_width, k_off, v_off
+    p.window = int(window or 0)
+    p.dtype = dtype_code(q.dtype)
+    p.scale = float(scale)
+    return p
+
+
+def attention_rows_plain(params: RowAttnParams):
+    _l.check(_l.load().dk_attention_rows_plain(C.byref(params), _stream()), "attention_rows_plain")
+
+
+def rows_append(src, tok_pos, tok_row, block_table, cache, *, H, KV, dk, dv, ps, row_width, k_off, v_off, table=None,
+                rot_dims=0, interleaved=True, err=None):
+    """``src`` [T, (H+KV)*dk + KV*dv] holds q, k and v of every token.  q and k get rotary positions on the first
+    ``rot_dims`` entries of each head (``table`` [positions, rot_dims/2, 2] of cos and sin; None: none), q in place;
+    k and v are written to the token's rows of ``cache`` [pages, KV, ps, row_width] (None: nothing is appended)."""
+    T = src.shape[0]
+    if cache is not None and (tuple(cache.shape[1:]) != (KV, ps, row_width) or cache.dtype != src.dtype):
+        raise KernelError(f"rows_append: cache has shape {tuple(cache.shape)} / {cache.dtype}, expected [pages, {KV}, {ps}, {row_width}] of {src.dtype}")
+    if table is not None and tuple(table.shape[1:]) != (rot_dims // 2, 2):
+        raise KernelError(f"rows_append: table has shape {tuple(table.shape)}, expected [positions, {rot_dims // 2}, 2]")
+    i32 = torch.int32
+    _l.check(_l.load().dk_rows_append(
+        _ptr(src, "src"), src.shape[1], _ptr(tok_pos, "tok_pos", i32), _ptr(tok_row, "tok_row", i32),
+        _ptr(block_table, "block_table", i32), block_table.shape[1] if block_table is not None else 0, _ptr(cache, "cache"),
+        cache.shape[0] if cache is not None else 0, _ptr(table, "table", torch.float32), table.shape[0] if table is not None else 0,
+        int(rot_dims), int(bool(interleaved)), T, H, KV, dk, dv, ps, row_width, k_off, v_off, dtype_code(src.dtype),
+        _ptr(err, "err", i32), _stream()), "rows_append")
+
+
+def latent_prepare(src, tok_pos, tok_row, block_table, cache, qabs, *, norm_weight, eps, H, dq, dr, R, ps, table=None, rot_dims=0,
+                   interleaved=True, err=None):
+    """``src`` [T, H*(dq+dr) + R + dr]: per head the plain and the rotated query part, then the latent and the shared
+    rotated key part.  Writes the normalised latent and the rotated key part to the token's row of ``cache``
+    [pages, 1, ps, R+dr] and the heads' rotated query parts to ``qabs`` [T, H, R+dr] at [R, R+dr)."""
+    T = src.shape[0]
+    if cache is not None and (tuple(cache.shape[1:]) != (1, ps, R + dr) or cache.dtype != src.dtype):
+        raise KernelError(f"latent_prepare: cache has shape {tuple(cache.shape)} / {cache.dtype}, expected [pages, 1, {ps}, {R + dr}] of {src.dtype}")
+    if tuple(qabs.shape) != (T, H, R + dr):
+        raise KernelError(f"latent_prepare: qabs has shape {tuple(qabs.shape)}, expected {(T, H, R + dr)}")
+    i32 = torch.int32
+    _l.check(_l.load().dk_latent_prepare(
+        _ptr(src, "src"), src.shape[1], _ptr(tok_pos, "tok_pos", i32), _ptr(tok_row, "tok_row", i32),
+        _ptr(block_table, "block_table", i32), block_table.shape[1] if block_table is not None else 0, _ptr(cache, "cache"),
+        cache.shape[0] if cache is not None else 0, _ptr(table, "table", torch.float32), table.shape[0] if table is not None else 0,
+        int(rot_dims), int(bool(interleaved)), _ptr(norm_weight, "norm_weight", torch.float32), float(eps),
+        _ptr(qabs, "qabs", src.dtype), T, H, dq, dr, R, ps, dtype_code(src.dtype), _ptr(err, "err", i32), _stream()), "latent_prepare")
+
+
+def gemm_nt_plain_batched(a_ptr, w_ptr, c_ptr, M, N, K, lda, ldw, ldc, batch, sa, sw, sc, in_dtype, out_dtype):
+    """``batch`` products C_b[M,N] = A_b[M,K] W_b[N,K]^T on the FMA units with float accumulation; the operands of product b
+    lie b*sa, b*sw and b*sc elements behind the given addresses (raw addresses: the operands may be interleaved views)."""
+    _l.check(_l.load().dk_gemm_nt_plain_batched(a_ptr, w_ptr, c_ptr, M, N, K, lda, ldw, ldc, batch, sa, sw, sc,
+                                                dtype_code(in_dtype), dtype_code(out_dtype), _stream()), "gemm_nt_plain_batched")
+
+
+def attention_rows_mma_supported(params: RowAttnParams) -> bool:
+    return False
+
+
+def attention_rows_decode_supported(params: RowAttnParams) -> bool:
+    return False

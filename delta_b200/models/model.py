@@ -14,7 +14,8 @@ import torch
 
 from ..kernels import ops
 from ..parts import linear
-from ..parts.base import BLOCKS, NORMS, CacheSpec, StateSpec, TensorSpec
+from ..parts.base import BLOCKS, NORMS, STREAMS, CacheSpec, RunState, StateSpec, TensorSpec
+from ..parts import streams as _streams  # noqa: F401  (registers the streams)
 from .spec import ModelSpec, RunEntry
 
 
@@ -25,6 +26,7 @@ class Model:
         for ls in spec.layers:
             self.blocks.append(BLOCKS.create(ls.block, parts={role: ps.build() for role, ps in ls.parts.items()}))
         self.final_norm = spec.final_norm.build(NORMS)
+        self.stream = spec.stream.build(STREAMS) if spec.stream is not None else STREAMS.create("single", width=spec.width)
         self.embed_table = None
         self.lm_head = None
         # run order with every entry's cache index resolved
@@ -41,6 +43,7 @@ class Model:
         for b in self.blocks:
             yield from b.parts()
         yield self.final_norm
+        yield self.stream
 
     def tensor_specs(self) -> List[TensorSpec]:
         specs = [self.spec.embedding]
@@ -81,23 +84,46 @@ class Model:
                 if k in out and out[k] != s:
                     raise ValueError(f"two parts declare the state '{k}' with different layouts")
                 out[k] = s
+        for e in self.order:       # state per run of a layer: every run has tensors of its own
+            for name, s in self.blocks[e.layer].run_state_specs().items():
+                out[self.run_state_key(e.cache, name)] = s
         return out
+
+    @staticmethod
+    def run_state_key(cache_id: int, name: str) -> str:
+        return f"run{cache_id}.{name}"
+
+    def has_run_state(self) -> bool:
+        """True when some layer carries a recurrent state from step to step: a step that ran cannot be run again
+        from the same start, unlike one that only appended keys and values."""
+        return any(self.blocks[e.layer].run_state_specs() for e in self.order)
 
     # ---- a step -------------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor:
         """Runs the tokens of ``ctx`` and returns float32 logits [len(ctx.logit_rows), vocab]."""
-        T = ctx.num_tokens
-        x = torch.empty((T, self.spec.width), dtype=ctx.dtype, device=ctx.device)
-        ops.embedding(ctx.tokens, self.embed_table, x, err=ctx.err)
+        x = self.stream.start(ctx, self.embed_table)
         for p in self.parts():
             p.begin_step(ctx)
         pending = None
+        totals = ctx.capture.get("layer_totals") if ctx.capture is not None else None
         for e in self.order:
             block = self.blocks[e.layer]
             cache = ctx.cache_view(e.cache, e.writes_cache) if block.cache_spec() is not None else None
+            names = block.run_state_specs()
+            if names:
+                state = {n: ctx.state(self.run_state_key(e.cache, n)) for n in names}
+                if cache is None:
+                    cache = RunState(state, e.writes_cache)
+                else:
+                    cache.state = state
             x, pending = block.forward(ctx, x, pending, cache)
+            if totals is not None:      # for tests: the settled stream after every run of a layer
+                totals.append(self.stream.total(ctx, x, pending))
         R = ctx.logit_rows.shape[0]
         if R == 0:      # nothing reads the stream after the last layer
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
-        h = self.final_norm.forward(ctx, x, add=pending, rows=ctx.logit_rows)
-        return linear.linear(ctx, h, self.lm_head, out_dtype=torch.float32)
+        h = self.stream.finish(ctx, x, pending, self.final_norm, ctx.logit_rows)
+        logits = linear.linear(ctx, h, self.lm_head, out_dtype=torch.float32)
+        if self.spec.logit_softcap:
+            ops.softcap(logits, self.spec.logit_softcap)
+        return logits

@@ -39,6 +39,8 @@ class ModelSpec:
     embedding: TensorSpec
     lm_head: TensorSpec
     max_positions: int = 0
+    stream: Optional[PartSpec] = None       # the residual stream (None: one copy in the compute type)
+    logit_softcap: Optional[float] = None   # logits <- cap * tanh(logits / cap)
     ignorable_tensors: tuple = ()   # shell patterns of tensor names a model folder may hold beside the ones asked for
 
     def __post_init__(self):

@@ -135,6 +135,16 @@ class Mixer(Part):
         raise NotImplementedError
 
 
+class RunState:
+    """What a mixer with a recurrent state gets for one run of its layer: ``state[name]`` is the tensor
+    [slots, *shape] of the state it declared under that name in ``run_state_specs`` (every run of a layer has
+    tensors of its own, so a layer that runs several times in a pass keeps one state per run)."""
+
+    def __init__(self, state: Dict[str, torch.Tensor], writes: bool = True):
+        self.state = state
+        self.writes = writes
+
+
 class FeedForward(Part):
     """``forward(ctx, x)``: rows [T, d] to rows [T, d], token by token."""
 
@@ -151,13 +161,17 @@ class Block(Part):
     same pair."""
 
     roles: tuple = ()
+    optional_roles: tuple = ()      # roles a layer may leave out (their attributes are None then)
 
     def __init__(self, parts: Dict[str, Part]):
         missing = [r for r in self.roles if r not in parts]
-        extra = [r for r in parts if r not in self.roles]
+        extra = [r for r in parts if r not in self.roles and r not in self.optional_roles]
         if missing or extra:
-            raise ValueError(f"{type(self).__name__} takes the parts {list(self.roles)}; missing {missing}, not taken {extra}")
+            raise ValueError(f"{type(self).__name__} takes the parts {list(self.roles)} and may take {list(self.optional_roles)}; "
+                             f"missing {missing}, not taken {extra}")
         self._parts = dict(parts)
+        for role in self.optional_roles:
+            setattr(self, role, None)
         for role, part in parts.items():
             setattr(self, role, part)
 
@@ -172,7 +186,33 @@ class Block(Part):
                 return cs
         return None
 
+    def run_state_specs(self) -> Dict[str, StateSpec]:
+        """The per-run state of its parts (see ``Mixer.run_state_specs``)."""
+        out: Dict[str, StateSpec] = {}
+        for p in self._parts.values():
+            if hasattr(p, "run_state_specs"):
+                out.update(p.run_state_specs())
+        return out
+
     def forward(self, ctx, x, pending, cache):
+        raise NotImplementedError
+
+
+class Stream(Part):
+    """The residual stream of a model: how it starts from the embedding table, what a block hands on as ``pending``
+    means, and how it ends in the rows the output matrix reads.
+
+    ``start(ctx, table)`` returns the stream tensor of the step's tokens; ``finish(ctx, x, pending, norm, rows)`` returns
+    the normalised rows [len(rows), d] in the compute type; ``total(ctx, x, pending)`` returns the settled stream
+    [T, d] in float32 (for inspection: what the layers so far have summed up)."""
+
+    def start(self, ctx, table):
+        raise NotImplementedError
+
+    def finish(self, ctx, x, pending, norm, rows):
+        raise NotImplementedError
+
+    def total(self, ctx, x, pending):
         raise NotImplementedError
 
 
@@ -215,16 +255,18 @@ POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 BLOCKS = Registry("block")
+STREAMS = Registry("residual stream")
+STREAM_MIXINGS = Registry("stream mixing")
 
 
 REGISTRIES = {"norm": NORMS, "position": POSITION_ENCODINGS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS,
-              "block": BLOCKS}
+              "block": BLOCKS, "stream": STREAMS, "stream_mixing": STREAM_MIXINGS}
 
 
 @dataclass(frozen=True)
 class PartSpec:
     """Registry name of a part, its parameters, and the registry it is looked up in
-    ("norm", "position", "mixer", "feed_forward", "block")."""
+    ("norm", "position", "mixer", "feed_forward", "block", "stream", "stream_mixing")."""
     kind: str
     params: dict = field(default_factory=dict)
     category: str = ""

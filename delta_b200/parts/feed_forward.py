@@ -38,3 +38,30 @@ class SwiGLU(FeedForward):
             act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
             ops.silu_mul(gu, act)
         return linear.linear(ctx, act, self.w_down)
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(FeedForward):
+    """down( act(up x) ) with ``activation`` one of "relu2" (the square of relu), "gelu_tanh", "silu".  Tensor names:
+    ``<prefix><up_name>`` [I, d] and ``<prefix><down_name>`` [d, I]."""
+
+    def __init__(self, prefix: str, width: int, intermediate: int, activation: str = "relu2", up_name: str = "up",
+                 down_name: str = "down"):
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation '{activation}'; known: {', '.join(ops.ACTIVATIONS)}")
+        self.prefix, self.width, self.intermediate, self.activation = prefix, int(width), int(intermediate), activation
+        self.up_name, self.down_name = up_name, down_name
+        self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        p, d, i = self.prefix, self.width, self.intermediate
+        return [TensorSpec(p + self.up_name, (i, d)), TensorSpec(p + self.down_name, (d, i))]
+
+    def bind(self, tensors):
+        self.w_up = tensors[self.prefix + self.up_name]
+        self.w_down = tensors[self.prefix + self.down_name]
+
+    def forward(self, ctx, x):
+        h = linear.linear(ctx, x, self.w_up)
+        ops.activation(h, h, self.activation)
+        return linear.linear(ctx, h, self.w_down)

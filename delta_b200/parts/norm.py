@@ -20,12 +20,20 @@ class RMSNorm(Norm):
         self.eps = float(eps)
         self.cast_before_weight = bool(cast_before_weight)
         self.weight = None
+        self._weight32 = None
 
     def tensor_specs(self):
         return [TensorSpec(self.name, (self.width,), kind="vector", init="norm")]
 
     def bind(self, tensors):
         self.weight = tensors[self.name]
+        self._weight32 = None
+
+    def weight32(self):
+        """The weight in 32 bit, for kernels that normalise a 32-bit stream."""
+        if self._weight32 is None:
+            self._weight32 = self.weight.float().contiguous()
+        return self._weight32
 
     def forward(self, ctx, x, add=None, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]

@@ -1,0 +1,110 @@
+"""Attention over a paged cache of rows: every cached token of a key-value head is one row that holds its key
+and its value, of sizes that may differ (``csrc/row_attention_params.h``).
+
+``sink_attention``: grouped-query attention, H query heads on ``kv_heads`` key-value heads (query head h reads
+key-value head h // (H / kv_heads)), with the options
+  * ``window`` W: position i sees the keys j with i - W < j <= i (None: every j <= i);
+  * ``sink``: a learned logit per head that joins the softmax's denominator and carries no value,
+        p_j = exp(s_j) / (exp(sink_h) + sum_j' exp(s_j'));
+  * ``position``: a rotary position encoding on the first ``rot_dims`` entries of every query and key head
+    (None: positions do not enter the scores);
+  * ``scale``: the factor on q . k (default 1 / sqrt(head_dim)).
+Scores and softmax weights are 32 bit in every kernel of the family.  ``run`` chooses the kernels for a batch.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from . import linear
+from .base import MIXERS, PAGE, POSITION_ENCODINGS, CacheSpec, Mixer, PartSpec, TensorSpec
+
+
+def plain(ctx) -> bool:
+    return "attention" in ctx.plain_kernels or ctx.dtype != torch.bfloat16
+
+
+def run(ctx, params) -> None:
+    """Runs attention over a cache of rows with the kernels that fit the batch: bfloat16 rows that bring several
+    tokens go to the tiled tensor-core kernel, rows that bring one token to the split-key kernel; 32 bit and sizes
+    those kernels do not take go to the plain kernel."""
+    if not plain(ctx):
+        fast_prefill = ops.attention_rows_mma_supported(params)
+        fast_decode = ops.attention_rows_decode_supported(params)
+        singles = ctx.decode_only or any(n == 1 for n in ctx.host["q_lens"])
+        several = not ctx.decode_only
+        if (not singles or fast_decode) and (not several or fast_prefill):
+            if singles:
+                params.row_filter = 1 if several else 0
+                ops.attention_rows_decode(params, ctx)
+            if several:
+                params.row_filter = 2 if singles else 0
+                ops.attention_rows_mma(params, ctx.max_q_len)
+            return
+    params.row_filter = 0
+    ops.attention_rows_plain(params)
+
+
+def make_params(ctx, *, q, q_stride, q_head_stride, out, cache, H, KV, dk, dv, row_width, k_off, v_off, scale, window=None,
+                sink=None):
+    return ops.row_attn_params(
+        q=q, q_stride=q_stride, q_head_stride=q_head_stride, out=out, cache=cache.pages, block_table=cache.block_table,
+        tok_row=ctx.tok_row, tok_pos=ctx.tok_pos, row_q_start=ctx.row_q_start, row_q_len=ctx.row_q_len,
+        row_pos_start=ctx.row_pos_start, H=H, KV=KV, dk=dk, dv=dv, ps=cache.page_size, row_width=row_width, k_off=k_off,
+        v_off=v_off, scale=scale, window=window or 0, sink=sink, err=ctx.err)
+
+
+@MIXERS.register("sink_attention")
+class SinkAttention(Mixer):
+    """Tensor names: ``<prefix><q|k|v|o>`` (``names`` replaces them) and ``<prefix>sink`` [heads] when ``sink``."""
+
+    def __init__(self, prefix: str, width: int, heads: int, kv_heads: int, head_dim: int, value_dim: Optional[int] = None,
+                 window: Optional[int] = None, sink: bool = False, scale: Optional[float] = None,
+                 position: Optional[PartSpec] = None, rot_dims: Optional[int] = None, names: Optional[dict] = None):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} heads are no multiple of {kv_heads} key-value heads")
+        self.prefix, self.width = prefix, int(width)
+        self.heads, self.kv_heads, self.dk = int(heads), int(kv_heads), int(head_dim)
+        self.dv = int(value_dim) if value_dim else self.dk
+        self.window = int(window) if window else None
+        self.has_sink = bool(sink)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.dk)
+        self.position = position.build(POSITION_ENCODINGS) if position is not None else None
+        self.rot_dims = int(rot_dims) if rot_dims else (self.dk if position is not None else 0)
+        self.names = dict(q="q", k="k", v="v", o="o", sink="sink")
+        self.names.update(names or {})
+        self.w_qkv = self.w_o = self.sink = None
+
+    def tensor_specs(self):
+        p, n, d = self.prefix, self.names, self.width
+        specs = [TensorSpec(p + n["q"], (self.heads * self.dk, d)), TensorSpec(p + n["k"], (self.kv_heads * self.dk, d)),
+                 TensorSpec(p + n["v"], (self.kv_heads * self.dv, d)), TensorSpec(p + n["o"], (d, self.heads * self.dv))]
+        if self.has_sink:
+            specs.append(TensorSpec(p + n["sink"], (self.heads,), kind="vector", init="uniform:-1:1"))
+        return specs
+
+    def bind(self, tensors):
+        p, n = self.prefix, self.names
+        self.w_qkv = torch.cat([tensors[p + n["q"]], tensors[p + n["k"]], tensors[p + n["v"]]], dim=0).contiguous()
+        self.w_o = tensors[p + n["o"]]
+        self.sink = tensors[p + n["sink"]].float().contiguous() if self.has_sink else None
+
+    def cache_spec(self):
+        # a page of a layer: [kv head][offset in the page][key | value]
+        return CacheSpec((self.kv_heads, PAGE, self.dk + self.dv), self.window, run_tokens=128)
+
+    def forward(self, ctx, x, cache):
+        H, KV, dk, dv = self.heads, self.kv_heads, self.dk, self.dv
+        qkv = linear.linear(ctx, x, self.w_qkv)
+        table = self.position.table(x.device) if self.position is not None else None
+        ops.rows_append(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, cache.pages if cache.writes else None, H=H, KV=KV,
+                        dk=dk, dv=dv, ps=cache.page_size, row_width=dk + dv, k_off=0, v_off=dk, table=table,
+                        rot_dims=self.rot_dims, interleaved=bool(getattr(self.position, "interleaved", True)), err=ctx.err)
+        out = torch.empty((x.shape[0], H * dv), dtype=x.dtype, device=x.device)
+        params = make_params(ctx, q=qkv, q_stride=qkv.shape[1], q_head_stride=dk, out=out, cache=cache, H=H, KV=KV, dk=dk, dv=dv,
+                             row_width=dk + dv, k_off=0, v_off=dk, scale=self.scale, window=self.window, sink=self.sink)
+        run(ctx, params)
+        return linear.linear(ctx, out, self.w_o)

@@ -27,6 +27,13 @@ def _draw(spec: TensorSpec, gen: torch.Generator, device) -> torch.Tensor:
         return 1.0 + (torch.rand(spec.shape, generator=gen, device=device, dtype=torch.float32) * 0.2 - 0.1)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, device=device, dtype=torch.float32)
+    if spec.init.startswith("uniform:"):      # "uniform:a:b": U(a, b)
+        a, b = (float(v) for v in spec.init.split(":")[1:3])
+        return a + (b - a) * torch.rand(spec.shape, generator=gen, device=device, dtype=torch.float32)
+    if spec.init.startswith("eye:"):          # "eye:r": the unit matrix + U(-r, r)
+        r = float(spec.init.split(":")[1])
+        eye = torch.eye(spec.shape[0], spec.shape[1], device=device, dtype=torch.float32)
+        return eye + r * (2.0 * torch.rand(spec.shape, generator=gen, device=device, dtype=torch.float32) - 1.0)
     raise ValueError(f"unknown init '{spec.init}' of tensor {spec.name}")
 
 
