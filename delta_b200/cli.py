@@ -111,7 +111,7 @@ def main(argv=None) -> int:
         tok = AutoTokenizer.from_pretrained(args.model_name, local_files_only=True)
         eng.set_tokenizer(tok)
 
-    vocab = int(config_json["vocab_size"])
+    vocab = eng.runner.vocab_size
     if args.dataset == "random":
         rng = random.Random(args.seed)
         prompts = [[rng.randrange(vocab) for _ in range(args.prompt_len)] for _ in range(args.num_samples)]

@@ -1,4 +1,5 @@
 from .engine_config import EngineConfig
 from .selective_cache import SelectiveCacheConfig
 from .model_config import ConfigError, YiConfig
+from .roletar_config import RoletarConfig
 from .registry import ARCHITECTURES, Architecture, architecture_of, read_config, register_architecture, unregister_architecture

@@ -246,6 +246,9 @@ class LMBackend:
             return
         if not runner.decode_graph_ready(len(plan)):
             return
+        if runner.model.has_run_state():
+            # a step launched ahead may have to be dropped and run again; one that advanced a recurrent state cannot be
+            return
         limit = runner.cache.max_seq_len
         for x in plan:
             r = x.request
