@@ -1,0 +1,321 @@
+// Paged attention over a cache of rows for bfloat16 on the tensor cores (warp-level MMA), for prompt portions and
+// for single decoded tokens alike.
+//
+// A block takes one (batch row, key-value head) and a tile of its "query rows": the pairs (new token i, head hh of
+// the group), numbered m = i * G + hh, so that every head that shares the key-value head shares the block's key
+// tiles.  With one shared head (a latent cache) a 64-row tile is a few tokens times all heads and the cache is
+// read once for all of them; a single decoded token is a tile of G rows.  Keys stream through shared memory in
+// tiles (cp.async, two stages, 16-byte chunks swizzled for ldmatrix); a cached row holds key and value, so one
+// copy brings both, and a value that is the front of its key is not copied twice.  Per tile and warp:
+// S = Q K^T (mma.sync.m16n8k16, float accumulators), mask by position (causal, window), online softmax in
+// float, O += P V.  The sink joins the denominator when the result is finished.
+//
+// grid (tiles of query rows, splits, batch rows * KV).  With more than one split each block takes a share of the
+// key tiles and stores (unnormalised O, running maximum, sum) per query row; a second kernel merges them.
+#include "common.cuh"
+#include "row_attention_params.h"
+#include "mma_helpers.cuh"
+
+namespace {
+constexpr int PSTAGES = 2;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__host__ __device__ inline int pad128(int bytes) { return (bytes + 127) / 128 * 128; }
+
+// part[((t*H + head) * splits + split) * (dv + 2)]: dv floats of O, then m (log2 units), then l
+template <int WARPS, int KT, int DVMAX>
+__global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const DkRowAttnParams p, float* __restrict__ part) {
+  constexpr int QT = 16 * WARPS, THREADS = WARPS * 32, NT = DVMAX / 8;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int row = blockIdx.z / p.KV, g = blockIdx.z % p.KV;
+  const int q_len = p.row_q_len[row];
+  if ((p.row_filter == 2 && q_len == 1) || (p.row_filter == 1 && q_len != 1)) return;
+  const int G = p.H / p.KV;
+  const int M = q_len * G;
+  const int m0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * QT;      // late tiles have the most keys: start them first
+  if (m0 >= M) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+  const int dk = p.dk, dv = p.dv, ps = p.ps;
+  const int KB = dk / 16;
+  const int ROWS = pad128(p.row_width * 2), QS = pad128(dk * 2);   // bytes between rows of a key tile / of the query tile
+  const int CPR = p.row_width / 8;                                  // 16-byte chunks of a cached row
+  unsigned char* q_smem = smem;
+  unsigned char* kv_smem = smem + QT * QS;
+  const int nrows = min(QT, M - m0);
+  const int q_start = p.row_q_start[row], pos_start = p.row_pos_start[row];
+  const int first_pos = pos_start + m0 / G, last_pos = pos_start + (m0 + nrows - 1) / G;
+  const int lo_tile = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
+  const int kt_lo = lo_tile / KT, kt_hi = last_pos / KT;
+  const int splits = gridDim.y, split = blockIdx.y;
+  const int per = (kt_hi - kt_lo + 1 + splits - 1) / splits;
+  const int kt_a = kt_lo + split * per, kt_b = min(kt_hi + 1, kt_a + per);   // this block's key tiles [kt_a, kt_b)
+  const __nv_bfloat16* cache = reinterpret_cast<const __nv_bfloat16*>(p.cache);
+  const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(p.q);
+
+  // the tile's query rows into shared memory
+  for (int c = tid; c < QT * (dk / 8); c += THREADS) {
+    const int r = c / (dk / 8), part_c = c % (dk / 8);
+    const int m = m0 + min(r, nrows - 1);
+    const __nv_bfloat16* src = q + (size_t)(q_start + m / G) * p.q_stride + (size_t)(g * G + m % G) * p.q_head_stride + part_c * 8;
+    cp_async_16(smem_u32(q_smem + r * QS + ((part_c ^ (r & 7)) * 16)), src, true);
+  }
+  auto load_tile = [&](int kt, int stage) {
+    unsigned char* dst = kv_smem + (size_t)stage * KT * ROWS;
+    for (int c = tid; c < KT * CPR; c += THREADS) {
+      const int tok = c / CPR, part_c = c % CPR;
+      const int key = kt * KT + tok;
+      bool valid = false;
+      size_t off = 0;
+      if (key <= last_pos && key >= lo_tile) {
+        const int lp = key / ps;
+        const int page = lp < p.max_pages ? p.block_table[(size_t)row * p.max_pages + lp] : -1;
+        if (page < 0 || page >= p.num_pages) {
+          if (part_c == 0) dk_report(p.err, DK_DEV_BAD_PAGE, q_start, lp, page);
+        } else {
+          valid = true;
+          off = (((size_t)page * p.KV + g) * ps + key % ps) * p.row_width + part_c * 8;
+        }
+      }
+      cp_async_16(smem_u32(dst + tok * ROWS + ((part_c ^ (tok & 7)) * 16)), cache + off, valid);
+    }
+  };
+
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  const float sc_log2 = p.scale * LOG2E;
+  // this thread's two query rows
+  const int r0 = warp * 16 + gq, r1 = r0 + 8;
+  const int mr0 = m0 + min(r0, nrows - 1), mr1 = m0 + min(r1, nrows - 1);
+  const int pos_r0 = pos_start + mr0 / G, pos_r1 = pos_start + mr1 / G;
+  const int warp_first_pos = pos_start + (m0 + min(warp * 16, nrows - 1)) / G;
+  const int warp_last_pos = pos_start + (m0 + min(warp * 16 + 15, nrows - 1)) / G;
+  const int kc0 = p.k_off / 8, vc0 = p.v_off / 8;
+
+  if (kt_a < kt_b) load_tile(kt_a, 0);
+  cp_async_commit();
+  for (int kt = kt_a; kt < kt_b; ++kt) {
+    if (kt + 1 < kt_b) load_tile(kt + 1, (kt + 1 - kt_a) % PSTAGES);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t kbase = smem_u32(kv_smem + (size_t)((kt - kt_a) % PSTAGES) * KT * ROWS);
+    const uint32_t qbase = smem_u32(q_smem);
+    const int kt0 = kt * KT;
+    const bool visible = warp * 16 < nrows && kt0 <= warp_last_pos && (p.window <= 0 || kt0 + KT - 1 > warp_first_pos - p.window);
+    if (visible) {
+      float s[KT / 8][4];
+#pragma unroll
+      for (int j = 0; j < KT / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      for (int kb = 0; kb < KB; kb += 2) {
+        uint32_t qa[4], qb[4];
+        {
+          const int r = warp * 16 + (lane & 15);
+          ldmatrix_x4(qa[0], qa[1], qa[2], qa[3], qbase + r * QS + (((2 * kb + (lane >> 4)) ^ (r & 7)) * 16));
+          if (kb + 1 < KB) ldmatrix_x4(qb[0], qb[1], qb[2], qb[3], qbase + r * QS + (((2 * kb + 2 + (lane >> 4)) ^ (r & 7)) * 16));
+        }
+#pragma unroll
+        for (int j = 0; j < KT / 8; ++j) {
+          const int tok = j * 8 + (lane & 7);
+          uint32_t b0, b1, b2, b3;
+          // (an odd count of 16-element blocks: the second pair of the last load repeats the first and is not used)
+          const int cj = kc0 + 2 * kb + (kb + 1 < KB ? (lane >> 3) : ((lane >> 3) & 1));
+          ldmatrix_x4(b0, b1, b2, b3, kbase + tok * ROWS + ((cj ^ (tok & 7)) * 16));
+          mma_bf16(s[j], qa, b0, b1);
+          if (kb + 1 < KB) mma_bf16(s[j], qb, b2, b3);
+        }
+      }
+      float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < KT / 8; ++j) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int key = kt0 + j * 8 + 2 * tq + c;
+          float v0 = s[j][c] * sc_log2, v1 = s[j][2 + c] * sc_log2;
+          if (key > pos_r0 || (p.window > 0 && key <= pos_r0 - p.window)) v0 = -INFINITY;
+          if (key > pos_r1 || (p.window > 0 && key <= pos_r1 - p.window)) v1 = -INFINITY;
+          s[j][c] = v0;
+          s[j][2 + c] = v1;
+          tmax[0] = fmaxf(tmax[0], v0);
+          tmax[1] = fmaxf(tmax[1], v1);
+        }
+      }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+        const float m_new = fmaxf(m_run[r], tmax[r]);
+        m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+        corr[r] = m_run[r] == -INFINITY ? 0.f : exp2f(m_run[r] - m_use[r]);
+        m_run[r] = m_new;
+        l_run[r] *= corr[r];
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        o[n][0] *= corr[0];
+        o[n][1] *= corr[0];
+        o[n][2] *= corr[1];
+        o[n][3] *= corr[1];
+      }
+#pragma unroll
+      for (int kb2 = 0; kb2 < KT / 16; ++kb2) {
+        uint32_t pa[4];
+        {
+          const float p00 = exp2f(s[2 * kb2][0] - m_use[0]), p01 = exp2f(s[2 * kb2][1] - m_use[0]);
+          const float p02 = exp2f(s[2 * kb2][2] - m_use[1]), p03 = exp2f(s[2 * kb2][3] - m_use[1]);
+          const float p10 = exp2f(s[2 * kb2 + 1][0] - m_use[0]), p11 = exp2f(s[2 * kb2 + 1][1] - m_use[0]);
+          const float p12 = exp2f(s[2 * kb2 + 1][2] - m_use[1]), p13 = exp2f(s[2 * kb2 + 1][3] - m_use[1]);
+          l_run[0] += p00 + p01 + p10 + p11;
+          l_run[1] += p02 + p03 + p12 + p13;
+          pa[0] = pack_bf16(p00, p01);
+          pa[1] = pack_bf16(p02, p03);
+          pa[2] = pack_bf16(p10, p11);
+          pa[3] = pack_bf16(p12, p13);
+        }
+        const int tok = kb2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int n = 0; n < NT; n += 2) {
+          if (n * 8 < dv) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, kbase + tok * ROWS + (((vc0 + n + (lane >> 4)) ^ (tok & 7)) * 16));
+            mma_bf16(o[n], pa, b0, b1);
+            mma_bf16(o[n + 1], pa, b2, b3);
+          }
+        }
+      }
+    }
+    __syncthreads();   // every warp is done with this stage before the next load overwrites it
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = half ? r1 : r0;
+    if (r >= nrows) continue;
+    const int m = m0 + r;
+    const int t = q_start + m / G, head = g * G + m % G;
+    float mm = m_run[half], ll = l_run[half];
+    if (splits > 1) {
+      float* dst = part + (((size_t)t * p.H + head) * splits + split) * (dv + 2);
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+        if (n * 8 < dv) {
+          dst[n * 8 + 2 * tq] = o[n][2 * half];
+          dst[n * 8 + 2 * tq + 1] = o[n][2 * half + 1];
+        }
+      if (tq == 0) {
+        dst[dv] = mm;
+        dst[dv + 1] = ll;
+      }
+      continue;
+    }
+    float f = 1.f;
+    if (p.sink != nullptr) {      // the sink joins the denominator: a key with this logit and no value
+      const float s2 = p.sink[head] * LOG2E;
+      const float mf = fmaxf(mm, s2);
+      f = mm == -INFINITY ? 0.f : exp2f(mm - mf);
+      ll = ll * f + exp2f(s2 - mf);
+    }
+    const float inv = ll > 0.f ? f / ll : 0.f;
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)t * p.H + head) * dv;
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+      if (n * 8 < dv) *reinterpret_cast<uint32_t*>(orow + n * 8 + 2 * tq) = pack_bf16(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
+  }
+}
+
+// one block per (token of a single-token row, head): sums the splits' partial results
+__global__ void attention_rows_merge_kernel(const DkRowAttnParams p, const float* __restrict__ part, int splits) {
+  const int t = blockIdx.x, head = blockIdx.y;
+  const int row = p.tok_row[t];
+  const int q_len = p.row_q_len[row];
+  if ((p.row_filter == 2 && q_len == 1) || (p.row_filter == 1 && q_len != 1)) return;
+  const int dv = p.dv;
+  const float* src = part + ((size_t)t * p.H + head) * splits * (dv + 2);
+  float mf = p.sink != nullptr ? p.sink[head] * LOG2E : -INFINITY;
+  for (int s = 0; s < splits; ++s) mf = fmaxf(mf, src[(size_t)s * (dv + 2) + dv]);
+  float l = p.sink != nullptr ? exp2f(p.sink[head] * LOG2E - mf) : 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = src[(size_t)s * (dv + 2) + dv];
+    if (ms != -INFINITY) l += src[(size_t)s * (dv + 2) + dv + 1] * exp2f(ms - mf);
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)t * p.H + head) * dv;
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = src[(size_t)s * (dv + 2) + dv];
+      if (ms != -INFINITY) a = fmaf(src[(size_t)s * (dv + 2) + d], exp2f(ms - mf), a);
+    }
+    orow[d] = __float2bfloat16_rn(a * inv);
+  }
+}
+
+template <int WARPS, int KT, int DVMAX>
+int launch(const DkRowAttnParams& p, int m_tiles, int splits, float* part, cudaStream_t stream) {
+  const size_t smem = (size_t)16 * WARPS * pad128(p.dk * 2) + (size_t)PSTAGES * KT * pad128(p.row_width * 2);
+  if (smem > 220 * 1024) {
+    dk_set_error("attention_rows_mma: rows of %d elements need more shared memory than a block has", p.row_width);
+    return DK_ERR_ARG;
+  }
+  static size_t configured_on[DK_MAX_DEVICES] = {0};
+  size_t& configured = configured_on[dk_current_device()];
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_rows_mma_kernel<WARPS, KT, DVMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      dk_set_error("attention_rows_mma: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      return DK_ERR_LAUNCH;
+    }
+    configured = smem;
+  }
+  dim3 grid(m_tiles, splits, p.rows * p.KV);
+  attention_rows_mma_kernel<WARPS, KT, DVMAX><<<grid, WARPS * 32, smem, stream>>>(p, part);
+  return dk_check_launch("attention_rows_mma");
+}
+}  // namespace
+
+extern "C" int dk_attention_rows_mma_supported(const DkRowAttnParams* pp) {
+  const DkRowAttnParams& p = *pp;
+  if (p.dtype != DK_BF16 || p.KV <= 0 || p.H % p.KV != 0) return 0;
+  if (p.dk % 16 || p.dv % 16 || p.dk < 16 || p.dv < 16 || p.dv > 256) return 0;
+  if (p.row_width % 8 || p.k_off % 8 || p.v_off % 8 || p.q_stride % 8 || p.q_head_stride % 8) return 0;
+  if (p.ps < 1 || p.ps > 128 || (p.ps & (p.ps - 1)) != 0) return 0;
+  if ((size_t)64 * pad128(p.dk * 2) + (size_t)PSTAGES * 64 * pad128(p.row_width * 2) > 220 * 1024) return 0;
+  return 1;
+}
+
+// Floats of scratch that `splits` > 1 need.
+extern "C" long long dk_attention_rows_mma_scratch_floats(int T, int H, int dv, int splits) {
+  return splits > 1 ? (long long)T * H * splits * (dv + 2) : 0;
+}
+
+// max_m: the most query rows (tokens * heads of a group) any batch row brings among those the filter lets through.
+extern "C" int dk_attention_rows_mma(const DkRowAttnParams* pp, int max_m, int splits, float* part, cudaStream_t stream) {
+  const DkRowAttnParams& p = *pp;
+  if (p.T == 0 || p.rows == 0) return 0;
+  DK_REQUIRE(dk_attention_rows_mma_supported(pp), "attention_rows_mma: sizes not taken (bfloat16; key and value sizes multiples of 16, value "
+             "at most 256; offsets and strides multiples of 8): dk=%d dv=%d width=%d", p.dk, p.dv, p.row_width);
+  DK_REQUIRE(max_m >= 1 && splits >= 1 && splits <= 65535, "attention_rows_mma: bad max_m %d or splits %d", max_m, splits);
+  DK_REQUIRE(splits == 1 || part != nullptr, "attention_rows_mma: splits without scratch memory");
+  DK_REQUIRE(p.row_q_start && p.row_q_len && p.row_pos_start && p.tok_row, "attention_rows_mma: the rows' arrays are missing");
+  DK_REQUIRE((long long)p.rows * p.KV <= 65535, "attention_rows_mma: grid too large");
+  int e;
+  const bool small = max_m <= 16;
+#define GO(DVMAX) (small ? launch<1, 32, DVMAX>(p, 1, splits, part, stream) : launch<4, 64, DVMAX>(p, (max_m + 63) / 64, splits, part, stream))
+  if (p.dv <= 64) e = GO(64);
+  else if (p.dv <= 128) e = GO(128);
+  else e = GO(256);
+#undef GO
+  if (e != 0 || splits == 1) return e;
+  DK_REQUIRE(p.H <= 65535, "attention_rows_mma: too many heads");
+  attention_rows_merge_kernel<<<dim3(p.T, p.H), 128, 0, stream>>>(p, part, splits);
+  return dk_check_launch("attention_rows_merge");
+}

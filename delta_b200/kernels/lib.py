@@ -59,6 +59,8 @@ _SIGNATURES = {
     "dk_attention_rows_plain": [C.POINTER(RowAttnParams), P],
     "dk_rows_append": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
     "dk_latent_prepare": [P, I, P, P, P, I, P, I, P, I, I, I, P, F, P, I, I, I, I, I, I, I, P, P],
+    "dk_attention_rows_mma_supported": [C.POINTER(RowAttnParams)],
+    "dk_attention_rows_mma": [C.POINTER(RowAttnParams), I, I, P, P],
     "dk_gemm_nt_plain_batched": [P, P, P, I, I, I, I, I, I, I, L, L, L, I, I, P],
     "dk_embedding": [P, P, P, I, I, I, I, P, P],
     "dk_rms_norm": [P, P, P, P, P, I, I, F, I, I, I, P],
@@ -107,6 +109,8 @@ def load():
         lib.dk_gemm_stream_k_workspace_bytes.restype = C.c_longlong
         lib.dk_gemm_stream_k_workspace_bytes.argtypes = [I]
         lib.dk_sizeof_row_attn_params.restype = I
+        lib.dk_attention_rows_mma_scratch_floats.restype = C.c_longlong
+        lib.dk_attention_rows_mma_scratch_floats.argtypes = [I, I, I, I]
         if lib.dk_sizeof_row_attn_params() != C.sizeof(RowAttnParams):
             raise KernelError(f"RowAttnParams is {C.sizeof(RowAttnParams)} bytes in Python and "
                               f"{lib.dk_sizeof_row_attn_params()} in the library: the two declarations differ")

@@ -570,8 +570,16 @@ def gemm_nt_plain_batched(a_ptr, w_ptr, c_ptr, M, N, K, lda, ldw, ldc, batch, sa
 
 
 def attention_rows_mma_supported(params: RowAttnParams) -> bool:
-    return False
+    """True when the tensor-core kernel of the family takes these sizes (bfloat16; key and value sizes multiples of 16)."""
+    return bool(_l.load().dk_attention_rows_mma_supported(C.byref(params)))
 
 
-def attention_rows_decode_supported(params: RowAttnParams) -> bool:
-    return False
+def attention_rows_mma_scratch_floats(T, H, dv, splits) -> int:
+    return int(_l.load().dk_attention_rows_mma_scratch_floats(T, H, dv, splits))
+
+
+def attention_rows_mma(params: RowAttnParams, max_m: int, splits: int = 1, scratch=None):
+    """``max_m``: the most query rows (new tokens times heads of a group) of any batch row that ``params.row_filter`` lets
+    through.  ``splits`` > 1: that many blocks share a row's keys and ``scratch`` (float32) takes their partial results."""
+    _l.check(_l.load().dk_attention_rows_mma(C.byref(params), int(max_m), int(splits), _ptr(scratch, "scratch", torch.float32),
+                                             _stream()), "attention_rows_mma", 2 if splits > 1 else 1)

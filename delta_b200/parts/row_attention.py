@@ -23,29 +23,53 @@ from . import linear
 from .base import MIXERS, PAGE, POSITION_ENCODINGS, CacheSpec, Mixer, PartSpec, TensorSpec
 
 
+MAX_SPLITS = 32
+PARTIALS = "row_attention.partials"
+
+
 def plain(ctx) -> bool:
     return "attention" in ctx.plain_kernels or ctx.dtype != torch.bfloat16
 
 
+def decode_splits(rows: int, kv_heads: int, group: int, max_keys: int, sm_count: int) -> int:
+    """Blocks that share the keys of a (row, key-value head) in a step of single tokens: enough to fill the device about
+    twice, and so few that every block has two key tiles."""
+    small = group <= 16
+    blocks = max(1, rows * kv_heads * (1 if small else -(-group // 64)))
+    tiles = max(1, -(-max_keys // (32 if small else 64)))
+    return max(1, min(2 * sm_count // blocks, tiles // 2, MAX_SPLITS))
+
+
 def run(ctx, params) -> None:
-    """Runs attention over a cache of rows with the kernels that fit the batch: bfloat16 rows that bring several
-    tokens go to the tiled tensor-core kernel, rows that bring one token to the split-key kernel; 32 bit and sizes
-    those kernels do not take go to the plain kernel."""
-    if not plain(ctx):
-        fast_prefill = ops.attention_rows_mma_supported(params)
-        fast_decode = ops.attention_rows_decode_supported(params)
-        singles = ctx.decode_only or any(n == 1 for n in ctx.host["q_lens"])
-        several = not ctx.decode_only
-        if (not singles or fast_decode) and (not several or fast_prefill):
-            if singles:
-                params.row_filter = 1 if several else 0
-                ops.attention_rows_decode(params, ctx)
-            if several:
-                params.row_filter = 2 if singles else 0
-                ops.attention_rows_mma(params, ctx.max_q_len)
-            return
-    params.row_filter = 0
-    ops.attention_rows_plain(params)
+    """Runs attention over a cache of rows with the kernels that fit the batch.  bfloat16 with key and value sizes that
+    are multiples of 16 goes to the tensor-core kernel: rows that bring several tokens in tiles of 64 query rows, rows
+    that bring one token as a tile of their group's heads with the keys split over several blocks; a mixed step
+    launches it once for each kind.  32 bit and other sizes go to the plain kernel.  In a replayable step nothing is
+    chosen from the step's host data."""
+    if plain(ctx) or not ops.attention_rows_mma_supported(params):
+        params.row_filter = 0
+        ops.attention_rows_plain(params)
+        return
+    group = params.H // params.KV
+    singles = ctx.decode_only or any(n == 1 for n in ctx.host["q_lens"])
+    several = not ctx.decode_only
+    if singles:
+        params.row_filter = 1 if several else 0
+        splits, scratch = 1, None
+        if not several:
+            replay = getattr(ctx, "replayable", False)
+            longest = ctx.cache.max_seq_len if replay else ctx.max_seq_len
+            max_keys = min(longest, params.window + 64) if params.window else longest
+            rows = params.rows
+            splits = decode_splits(rows, params.KV, group, max_keys, ctx.sm_count)
+            if splits > 1:
+                n = ops.attention_rows_mma_scratch_floats(params.T, params.H, params.dv, splits)
+                bound = ops.attention_rows_mma_scratch_floats(max(getattr(ctx, "max_rows", 0), rows), params.H, params.dv, MAX_SPLITS)
+                scratch = ctx.scratch(PARTIALS + f".{params.dv}", (n,), torch.float32, bound=(bound,))
+        ops.attention_rows_mma(params, group, splits, scratch)
+    if several:
+        params.row_filter = 2 if singles else 0
+        ops.attention_rows_mma(params, ctx.max_q_len * group, 1, None)
 
 
 def make_params(ctx, *, q, q_stride, q_head_stride, out, cache, H, KV, dk, dv, row_width, k_off, v_off, scale, window=None,

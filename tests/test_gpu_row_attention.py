@@ -108,15 +108,17 @@ def run_case(dtype, plain, shape, row_lens, window=None, use_sink=False, latent=
     err = ops.new_error_record("cuda")
     ctx = Ctx(q_lens, dtype, plain)
     ctx.max_seq_len = max(b + n for b, n in row_lens)
-    params = ops.row_attn_params(
-        q=q, q_stride=H * dk, q_head_stride=dk, out=out, cache=cache.cuda(), block_table=bt.cuda(), tok_row=tok_row, tok_pos=tok_pos,
-        row_q_start=torch.tensor(starts, **i32), row_q_len=torch.tensor(q_lens, **i32),
-        row_pos_start=torch.tensor([b for b, _ in row_lens], **i32), H=H, KV=KV, dk=dk, dv=dv, ps=ps, row_width=row_width,
-        k_off=k_off, v_off=v_off, scale=scale, window=window or 0, sink=sink.cuda() if sink is not None else None, err=err)
+    # (the parameters hold raw addresses: every device tensor stays referenced until the result is read)
+    dev = dict(cache=cache.cuda(), block_table=bt.cuda(), row_q_start=torch.tensor(starts, **i32), row_q_len=torch.tensor(q_lens, **i32),
+               row_pos_start=torch.tensor([b for b, _ in row_lens], **i32), sink=sink.cuda() if sink is not None else None)
+    params = ops.row_attn_params(q=q, q_stride=H * dk, q_head_stride=dk, out=out, tok_row=tok_row, tok_pos=tok_pos, H=H, KV=KV, dk=dk,
+                                 dv=dv, ps=ps, row_width=row_width, k_off=k_off, v_off=v_off, scale=scale, window=window or 0, err=err,
+                                 **dev)
     ctx.err = err
     row_attention.run(ctx, params)
     ops.raise_if_error(err)
     got = out.float().cpu().view(-1, H, dv).double()
+    del dev
     worst = (got - want).abs().max().item()
     assert worst <= TOL[dtype] * max(1.0, want.abs().max().item()), f"differs by {worst:.3e}"
     return worst
