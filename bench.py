@@ -374,6 +374,158 @@ def other_workload(args) -> int:
     return 0
 
 
+def roletar_config(d: int) -> dict:
+    """A Roletar model with layers of the sizes of a real model of width d: a selective state-space layer, two latent
+    attention layers that run twice, a windowed attention layer with sinks; four residual streams."""
+    H = d // 128
+    ff = dict(kind="dense", ff=4 * d)
+    lat = dict(type="latent_attention", mlp=ff, mixer=dict(heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=256, scale=192 ** -0.5,
+                                                           rot=dict(base=10000.0, dims=64)))
+    return dict(architecture="Roletar", vocab=32000, width=d, streams=4, logit_softcap=30.0, norm=dict(eps=1e-6),
+                loop=dict(start=1, stop=3, times=2),
+                layers=[dict(type="mamba1", mlp=ff, mixer=dict(inner=2 * d, state=16, conv=4, dt_rank=d // 16)), lat, dict(lat),
+                        dict(type="attention", mlp=ff, mixer=dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, scale=128 ** -0.5,
+                                                                 mask=dict(size=1024)))])
+
+
+def yi_like_config(d: int, layers: int) -> dict:
+    """The closest existing model at equal size: as many layer runs, the same width and heads, a SwiGLU of equal weight count."""
+    return dict(YI_6B, hidden_size=d, num_hidden_layers=layers, num_attention_heads=d // 128, num_key_value_heads=max(1, d // 512),
+                intermediate_size=(8 * d // 3 + 255) // 256 * 256, vocab_size=32000, max_position_embeddings=8192)
+
+
+def roletar_workload(args) -> int:
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at context 2,048) of the Roletar design beside the
+    Yi architecture at equal width and layer count, through ``ModelRunner.step``, timed with CUDA events after warm-up with
+    the L2 flushed before every timed step; then every launcher's share of one such step, with the fraction of the measured
+    peaks that the design's own kernels and their Yi counterparts reach."""
+    import torch
+    from delta_b200.config import EngineConfig
+    from delta_b200.engine.step import ModelRunner, RowInput
+    from delta_b200.kernels import ops
+    pk = peaks()
+    T, B, CTX = 2048, 8, 2048
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")
+    gen = torch.Generator().manual_seed(1)
+    clocks = ClockSampler()
+    clocks.start()
+    out = {"workload": "roletar", "metric": "prefill tok/s and decode tok/s (Roletar beside Yi at equal width and layer runs, bf16)",
+           "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic token ids, random weights",
+           "steps": args.steps, "warmup": args.warmup, "peaks": pk, "sizes": {}}
+
+    def timed(fn, reps):
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    def measure(cfg_json, vocab):
+        ec = EngineConfig(max_batch=B + 1, max_seq_len=CTX + 64, page_size=16, dtype="bfloat16", max_tokens_per_step=T,
+                          num_pages=(B + 1) * (CTX + 64) // 16)
+        r = ModelRunner(config_json=cfg_json, seed=0, engine_config=ec)
+        prompt = torch.randint(0, vocab, (T,), generator=gen).tolist()
+        res = {}
+
+        def prefill():
+            slot = r.cache.acquire_slot()
+            r.run_rows([RowInput(slot, prompt, 0, [T - 1])])
+            r.cache.release_slot(slot)
+        for _ in range(max(3, args.warmup // 2)):
+            prefill()
+        res["prefill_ms"] = timed(prefill, max(3, args.steps // 8))
+        ops.profile_start()
+        prefill()
+        res["prefill_launchers"] = ops.profile_stop()
+        # decode: B requests at context CTX (filled in portions), then single tokens
+        slots = [r.cache.acquire_slot() for _ in range(B)]
+        for s in slots:
+            r.run_rows([RowInput(s, prompt[:CTX - 8], 0, [])])
+        pos = [CTX - 8]
+
+        def decode():
+            r.run_rows([RowInput(s, [7], pos[0], [0]) for s in slots])
+        for _ in range(3):
+            decode()
+            pos[0] += 1
+        res["decode_ms"] = timed(decode, max(3, args.steps // 8))     # (the same position is run again: equal work)
+        ops.profile_start()
+        decode()
+        res["decode_launchers"] = ops.profile_stop()
+        res["launches_per_decode_step"] = None
+        l0 = ops.launch_count()
+        decode()
+        res["launches_per_decode_step"] = ops.launch_count() - l0
+        del r
+        torch.cuda.empty_cache()
+        return res
+
+    launches = 0
+    for d in args.width:
+        rc = roletar_config(d)
+        runs = 6
+        yc = yi_like_config(d, runs)
+        a, b = measure(rc, rc["vocab"]), measure(yc, yc["vocab_size"])
+        launches += a["launches_per_decode_step"]
+        H = d // 128
+        # what the kernels of one step have to move or compute, per launcher (prefill of T tokens unless said otherwise)
+        S, C, N = 4, 2 * d, 16
+        work = {   # launcher: (bytes, flops) of ALL its calls in a prefill step
+            "stream_norm": ((2 * S * d * 4 + 2 * d * 2) * T * (2 * runs), 0),
+            "selective_scan": ((4 * C + 2 * N) * 2 * T, 0),
+            "conv_silu": (2 * C * 2 * T, 0),
+            "activation": (2 * 4 * d * 2 * T * runs, 0),
+            "latent_prepare": ((H * 192 + 320 + 320 + H * 64) * 2 * T * 4, 0),
+            "rows_append": ((H + 2 * max(1, H // 4)) * 128 * 2 * T, 0),
+            "gemm_nt_plain_batched": (0, 2 * T * H * (128 * 256 + 256 * 128) * 4),
+            "attention_rows_mma": (0, 4 * (2 * H * (320 + 256) * T * (T + 1) // 2) + 2 * H * 256 * (1024 * T - 1024 * 1023 // 2)),
+        }
+        yi_work = {
+            "rms_norm": (4 * d * 2 * T * (2 * runs) , 0),
+            "silu_mul": (3 * yc["intermediate_size"] * 2 * T * runs, 0),
+            "rope_append": ((H + 2 * max(1, d // 512)) * 128 * 2 * 2 * T * runs, 0),
+            "attention_prefill_tc": (0, 4 * 128 * H * (T * (T + 1) // 2) * runs),
+        }
+
+        def fractions(launchers, table):
+            rows = {}
+            for name, (calls, ms) in sorted(launchers.items(), key=lambda kv: -kv[1][1]):
+                row = {"calls": calls, "ms": round(ms, 4)}
+                if name in table and ms > 0:
+                    by, fl = table[name]
+                    if by:
+                        row["gbs"] = round(by / ms / 1e6, 1)
+                        row["of_measured_copy"] = round(by / ms / 1e6 / pk["hbm_gbs"], 3)
+                    if fl:
+                        row["tflops"] = round(fl / ms / 1e9, 1)
+                        row["of_measured_bf16"] = round(fl / ms / 1e9 / pk["bf16_tflops"], 3)
+                rows[name] = row
+            return rows
+        out["sizes"][str(d)] = {
+            "roletar": {"prefill_tok_s": T / a["prefill_ms"] * 1e3, "prefill_ms": a["prefill_ms"], "decode_tok_s": B / a["decode_ms"] * 1e3,
+                        "decode_ms": a["decode_ms"], "launches_per_decode_step": a["launches_per_decode_step"],
+                        "prefill_launchers": fractions(a["prefill_launchers"], work),
+                        "decode_launchers": fractions(a["decode_launchers"], {})},
+            "yi": {"prefill_tok_s": T / b["prefill_ms"] * 1e3, "prefill_ms": b["prefill_ms"], "decode_tok_s": B / b["decode_ms"] * 1e3,
+                   "decode_ms": b["decode_ms"], "launches_per_decode_step": b["launches_per_decode_step"],
+                   "prefill_launchers": fractions(b["prefill_launchers"], yi_work),
+                   "decode_launchers": fractions(b["decode_launchers"], {})},
+            "config": {"width": d, "layer_runs": runs, "prefill_tokens": T, "decode_batch": B, "decode_context": CTX,
+                       "l2": "flushed before every timed step"}}
+    first = out["sizes"][str(args.width[0])]
+    out.update(value=first["roletar"]["prefill_tok_s"], ms_per_step=first["roletar"]["prefill_ms"], vs_baseline=None,
+               gpu_launches=launches, clocks=clocks.stop(),
+               config={"model": f"Roletar, width {args.width[0]}, 6 layer runs", "global_batch": 1, "seq_len": T, "parallelism": "single GPU"})
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -389,7 +541,8 @@ def main() -> int:
     ap.add_argument("--enable_selective_cache", action="store_true", help="DELTA on (not the default run)")
     ap.add_argument("--full_cache_layers", nargs="+", type=int, default=[0, 1, 2, 14, 22])
     ap.add_argument("--subset_cache_size", type=int, default=64)
-    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown", "long-prompt"], default="decode")
+    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown", "long-prompt", "roletar"], default="decode")
+    ap.add_argument("--width", type=int, nargs="+", default=[2048, 4096], help="--workload roletar: the model widths that are measured")
     ap.add_argument("--generate", type=int, default=None, help="tokens generated per request in the other workloads (default: what the workload names)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -399,6 +552,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "roletar":
+        return roletar_workload(args)
     if args.workload != "decode":
         return other_workload(args)
 

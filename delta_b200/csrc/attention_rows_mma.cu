@@ -23,9 +23,11 @@ constexpr float LOG2E = 1.4426950408889634f;
 __host__ __device__ inline int pad128(int bytes) { return (bytes + 127) / 128 * 128; }
 
 // part[((t*H + head) * splits + split) * (dv + 2)]: dv floats of O, then m (log2 units), then l
-template <int WARPS, int KT, int DVMAX>
+// RM: 16-row tiles of query rows per warp.  With two, every key and value fragment that a warp fetches from shared memory
+// feeds two products, which is what bounds this kernel (it moves 512 bytes of fragments for every 2 x 4,096 FLOP product).
+template <int WARPS, int KT, int DVMAX, int RM>
 __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const DkRowAttnParams p, float* __restrict__ part) {
-  constexpr int QT = 16 * WARPS, THREADS = WARPS * 32, NT = DVMAX / 8;
+  constexpr int QT = 16 * WARPS * RM, THREADS = WARPS * 32, NT = DVMAX / 8, WR = 16 * RM;
   extern __shared__ __align__(128) unsigned char smem[];
   const int row = blockIdx.z / p.KV, g = blockIdx.z % p.KV;
   const int q_len = p.row_q_len[row];
@@ -80,18 +82,21 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
     }
   };
 
-  float o[NT][4];
+  float o[RM][NT][4];
+  float m_run[RM][2], l_run[RM][2];
+  int pos_r[RM][2];     // positions of this thread's query rows: rows warp*WR + rm*16 + gq and + 8
 #pragma unroll
-  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY};
-  float l_run[2] = {0.f, 0.f};
+  for (int rm = 0; rm < RM; ++rm) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[rm][n][0] = o[rm][n][1] = o[rm][n][2] = o[rm][n][3] = 0.f;
+    m_run[rm][0] = m_run[rm][1] = -INFINITY;
+    l_run[rm][0] = l_run[rm][1] = 0.f;
+    pos_r[rm][0] = pos_start + (m0 + min(warp * WR + rm * 16 + gq, nrows - 1)) / G;
+    pos_r[rm][1] = pos_start + (m0 + min(warp * WR + rm * 16 + gq + 8, nrows - 1)) / G;
+  }
   const float sc_log2 = p.scale * LOG2E;
-  // this thread's two query rows
-  const int r0 = warp * 16 + gq, r1 = r0 + 8;
-  const int mr0 = m0 + min(r0, nrows - 1), mr1 = m0 + min(r1, nrows - 1);
-  const int pos_r0 = pos_start + mr0 / G, pos_r1 = pos_start + mr1 / G;
-  const int warp_first_pos = pos_start + (m0 + min(warp * 16, nrows - 1)) / G;
-  const int warp_last_pos = pos_start + (m0 + min(warp * 16 + 15, nrows - 1)) / G;
+  const int warp_first_pos = pos_start + (m0 + min(warp * WR, nrows - 1)) / G;
+  const int warp_last_pos = pos_start + (m0 + min(warp * WR + WR - 1, nrows - 1)) / G;
   const int kc0 = p.k_off / 8, vc0 = p.v_off / 8;
 
   if (kt_a < kt_b) load_tile(kt_a, 0);
@@ -104,17 +109,21 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
     const uint32_t kbase = smem_u32(kv_smem + (size_t)((kt - kt_a) % PSTAGES) * KT * ROWS);
     const uint32_t qbase = smem_u32(q_smem);
     const int kt0 = kt * KT;
-    const bool visible = warp * 16 < nrows && kt0 <= warp_last_pos && (p.window <= 0 || kt0 + KT - 1 > warp_first_pos - p.window);
+    const bool visible = warp * WR < nrows && kt0 <= warp_last_pos && (p.window <= 0 || kt0 + KT - 1 > warp_first_pos - p.window);
     if (visible) {
-      float s[KT / 8][4];
+      float s[RM][KT / 8][4];
 #pragma unroll
-      for (int j = 0; j < KT / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      for (int rm = 0; rm < RM; ++rm)
+#pragma unroll
+        for (int j = 0; j < KT / 8; ++j) s[rm][j][0] = s[rm][j][1] = s[rm][j][2] = s[rm][j][3] = 0.f;
       for (int kb = 0; kb < KB; kb += 2) {
-        uint32_t qa[4], qb[4];
-        {
-          const int r = warp * 16 + (lane & 15);
-          ldmatrix_x4(qa[0], qa[1], qa[2], qa[3], qbase + r * QS + (((2 * kb + (lane >> 4)) ^ (r & 7)) * 16));
-          if (kb + 1 < KB) ldmatrix_x4(qb[0], qb[1], qb[2], qb[3], qbase + r * QS + (((2 * kb + 2 + (lane >> 4)) ^ (r & 7)) * 16));
+        uint32_t qa[RM][4], qb[RM][4];
+#pragma unroll
+        for (int rm = 0; rm < RM; ++rm) {
+          const int r = warp * WR + rm * 16 + (lane & 15);
+          ldmatrix_x4(qa[rm][0], qa[rm][1], qa[rm][2], qa[rm][3], qbase + r * QS + (((2 * kb + (lane >> 4)) ^ (r & 7)) * 16));
+          if (kb + 1 < KB)
+            ldmatrix_x4(qb[rm][0], qb[rm][1], qb[rm][2], qb[rm][3], qbase + r * QS + (((2 * kb + 2 + (lane >> 4)) ^ (r & 7)) * 16));
         }
 #pragma unroll
         for (int j = 0; j < KT / 8; ++j) {
@@ -123,66 +132,76 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
           // (an odd count of 16-element blocks: the second pair of the last load repeats the first and is not used)
           const int cj = kc0 + 2 * kb + (kb + 1 < KB ? (lane >> 3) : ((lane >> 3) & 1));
           ldmatrix_x4(b0, b1, b2, b3, kbase + tok * ROWS + ((cj ^ (tok & 7)) * 16));
-          mma_bf16(s[j], qa, b0, b1);
-          if (kb + 1 < KB) mma_bf16(s[j], qb, b2, b3);
+#pragma unroll
+          for (int rm = 0; rm < RM; ++rm) {
+            mma_bf16(s[rm][j], qa[rm], b0, b1);
+            if (kb + 1 < KB) mma_bf16(s[rm][j], qb[rm], b2, b3);
+          }
         }
       }
-      float tmax[2] = {-INFINITY, -INFINITY};
+      uint32_t pa[RM][KT / 16][4];
 #pragma unroll
-      for (int j = 0; j < KT / 8; ++j) {
+      for (int rm = 0; rm < RM; ++rm) {
+        float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int key = kt0 + j * 8 + 2 * tq + c;
-          float v0 = s[j][c] * sc_log2, v1 = s[j][2 + c] * sc_log2;
-          if (key > pos_r0 || (p.window > 0 && key <= pos_r0 - p.window)) v0 = -INFINITY;
-          if (key > pos_r1 || (p.window > 0 && key <= pos_r1 - p.window)) v1 = -INFINITY;
-          s[j][c] = v0;
-          s[j][2 + c] = v1;
-          tmax[0] = fmaxf(tmax[0], v0);
-          tmax[1] = fmaxf(tmax[1], v1);
+        for (int j = 0; j < KT / 8; ++j) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int key = kt0 + j * 8 + 2 * tq + c;
+            float v0 = s[rm][j][c] * sc_log2, v1 = s[rm][j][2 + c] * sc_log2;
+            if (key > pos_r[rm][0] || (p.window > 0 && key <= pos_r[rm][0] - p.window)) v0 = -INFINITY;
+            if (key > pos_r[rm][1] || (p.window > 0 && key <= pos_r[rm][1] - p.window)) v1 = -INFINITY;
+            s[rm][j][c] = v0;
+            s[rm][j][2 + c] = v1;
+            tmax[0] = fmaxf(tmax[0], v0);
+            tmax[1] = fmaxf(tmax[1], v1);
+          }
         }
-      }
-      float corr[2], m_use[2];
+        float corr[2], m_use[2];
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
-        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
-        const float m_new = fmaxf(m_run[r], tmax[r]);
-        m_use[r] = m_new == -INFINITY ? 0.f : m_new;
-        corr[r] = m_run[r] == -INFINITY ? 0.f : exp2f(m_run[r] - m_use[r]);
-        m_run[r] = m_new;
-        l_run[r] *= corr[r];
-      }
+        for (int r = 0; r < 2; ++r) {
+          tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+          tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+          const float m_new = fmaxf(m_run[rm][r], tmax[r]);
+          m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+          corr[r] = m_run[rm][r] == -INFINITY ? 0.f : exp2f(m_run[rm][r] - m_use[r]);
+          m_run[rm][r] = m_new;
+          l_run[rm][r] *= corr[r];
+        }
 #pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        o[n][0] *= corr[0];
-        o[n][1] *= corr[0];
-        o[n][2] *= corr[1];
-        o[n][3] *= corr[1];
+        for (int n = 0; n < NT; ++n) {
+          o[rm][n][0] *= corr[0];
+          o[rm][n][1] *= corr[0];
+          o[rm][n][2] *= corr[1];
+          o[rm][n][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kb2 = 0; kb2 < KT / 16; ++kb2) {
+          const float p00 = exp2f(s[rm][2 * kb2][0] - m_use[0]), p01 = exp2f(s[rm][2 * kb2][1] - m_use[0]);
+          const float p02 = exp2f(s[rm][2 * kb2][2] - m_use[1]), p03 = exp2f(s[rm][2 * kb2][3] - m_use[1]);
+          const float p10 = exp2f(s[rm][2 * kb2 + 1][0] - m_use[0]), p11 = exp2f(s[rm][2 * kb2 + 1][1] - m_use[0]);
+          const float p12 = exp2f(s[rm][2 * kb2 + 1][2] - m_use[1]), p13 = exp2f(s[rm][2 * kb2 + 1][3] - m_use[1]);
+          l_run[rm][0] += p00 + p01 + p10 + p11;
+          l_run[rm][1] += p02 + p03 + p12 + p13;
+          pa[rm][kb2][0] = pack_bf16(p00, p01);
+          pa[rm][kb2][1] = pack_bf16(p02, p03);
+          pa[rm][kb2][2] = pack_bf16(p10, p11);
+          pa[rm][kb2][3] = pack_bf16(p12, p13);
+        }
       }
 #pragma unroll
       for (int kb2 = 0; kb2 < KT / 16; ++kb2) {
-        uint32_t pa[4];
-        {
-          const float p00 = exp2f(s[2 * kb2][0] - m_use[0]), p01 = exp2f(s[2 * kb2][1] - m_use[0]);
-          const float p02 = exp2f(s[2 * kb2][2] - m_use[1]), p03 = exp2f(s[2 * kb2][3] - m_use[1]);
-          const float p10 = exp2f(s[2 * kb2 + 1][0] - m_use[0]), p11 = exp2f(s[2 * kb2 + 1][1] - m_use[0]);
-          const float p12 = exp2f(s[2 * kb2 + 1][2] - m_use[1]), p13 = exp2f(s[2 * kb2 + 1][3] - m_use[1]);
-          l_run[0] += p00 + p01 + p10 + p11;
-          l_run[1] += p02 + p03 + p12 + p13;
-          pa[0] = pack_bf16(p00, p01);
-          pa[1] = pack_bf16(p02, p03);
-          pa[2] = pack_bf16(p10, p11);
-          pa[3] = pack_bf16(p12, p13);
-        }
         const int tok = kb2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
         for (int n = 0; n < NT; n += 2) {
           if (n * 8 < dv) {
             uint32_t b0, b1, b2, b3;
             ldmatrix_x4_trans(b0, b1, b2, b3, kbase + tok * ROWS + (((vc0 + n + (lane >> 4)) ^ (tok & 7)) * 16));
-            mma_bf16(o[n], pa, b0, b1);
-            mma_bf16(o[n + 1], pa, b2, b3);
+#pragma unroll
+            for (int rm = 0; rm < RM; ++rm) {
+              mma_bf16(o[rm][n], pa[rm][kb2], b0, b1);
+              mma_bf16(o[rm][n + 1], pa[rm][kb2], b2, b3);
+            }
           }
         }
       }
@@ -192,43 +211,44 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
   cp_async_wait<0>();
 
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-  }
+  for (int rm = 0; rm < RM; ++rm) {
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int r = half ? r1 : r0;
-    if (r >= nrows) continue;
-    const int m = m0 + r;
-    const int t = q_start + m / G, head = g * G + m % G;
-    float mm = m_run[half], ll = l_run[half];
-    if (splits > 1) {
-      float* dst = part + (((size_t)t * p.H + head) * splits + split) * (dv + 2);
+    for (int half = 0; half < 2; ++half) {
+      float ll = l_run[rm][half];
+      ll += __shfl_xor_sync(0xffffffffu, ll, 1);
+      ll += __shfl_xor_sync(0xffffffffu, ll, 2);
+      const int r = warp * WR + rm * 16 + gq + 8 * half;
+      if (r >= nrows) continue;
+      const int m = m0 + r;
+      const int t = q_start + m / G, head = g * G + m % G;
+      const float mm = m_run[rm][half];
+      if (splits > 1) {
+        float* dst = part + (((size_t)t * p.H + head) * splits + split) * (dv + 2);
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+          if (n * 8 < dv) {
+            dst[n * 8 + 2 * tq] = o[rm][n][2 * half];
+            dst[n * 8 + 2 * tq + 1] = o[rm][n][2 * half + 1];
+          }
+        if (tq == 0) {
+          dst[dv] = mm;
+          dst[dv + 1] = ll;
+        }
+        continue;
+      }
+      float f = 1.f;
+      if (p.sink != nullptr) {      // the sink joins the denominator: a key with this logit and no value
+        const float s2 = p.sink[head] * LOG2E;
+        const float mf = fmaxf(mm, s2);
+        f = mm == -INFINITY ? 0.f : exp2f(mm - mf);
+        ll = ll * f + exp2f(s2 - mf);
+      }
+      const float inv = ll > 0.f ? f / ll : 0.f;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)t * p.H + head) * dv;
 #pragma unroll
       for (int n = 0; n < NT; ++n)
-        if (n * 8 < dv) {
-          dst[n * 8 + 2 * tq] = o[n][2 * half];
-          dst[n * 8 + 2 * tq + 1] = o[n][2 * half + 1];
-        }
-      if (tq == 0) {
-        dst[dv] = mm;
-        dst[dv + 1] = ll;
-      }
-      continue;
+        if (n * 8 < dv) *reinterpret_cast<uint32_t*>(orow + n * 8 + 2 * tq) = pack_bf16(o[rm][n][2 * half] * inv, o[rm][n][2 * half + 1] * inv);
     }
-    float f = 1.f;
-    if (p.sink != nullptr) {      // the sink joins the denominator: a key with this logit and no value
-      const float s2 = p.sink[head] * LOG2E;
-      const float mf = fmaxf(mm, s2);
-      f = mm == -INFINITY ? 0.f : exp2f(mm - mf);
-      ll = ll * f + exp2f(s2 - mf);
-    }
-    const float inv = ll > 0.f ? f / ll : 0.f;
-    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)t * p.H + head) * dv;
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
-      if (n * 8 < dv) *reinterpret_cast<uint32_t*>(orow + n * 8 + 2 * tq) = pack_bf16(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
   }
 }
 
@@ -259,9 +279,10 @@ __global__ void attention_rows_merge_kernel(const DkRowAttnParams p, const float
   }
 }
 
-template <int WARPS, int KT, int DVMAX>
-int launch(const DkRowAttnParams& p, int m_tiles, int splits, float* part, cudaStream_t stream) {
-  const size_t smem = (size_t)16 * WARPS * pad128(p.dk * 2) + (size_t)PSTAGES * KT * pad128(p.row_width * 2);
+template <int WARPS, int KT, int DVMAX, int RM>
+int launch(const DkRowAttnParams& p, int max_m, int splits, float* part, cudaStream_t stream) {
+  const int m_tiles = (max_m + 16 * WARPS * RM - 1) / (16 * WARPS * RM);
+  const size_t smem = (size_t)16 * WARPS * RM * pad128(p.dk * 2) + (size_t)PSTAGES * KT * pad128(p.row_width * 2);
   if (smem > 220 * 1024) {
     dk_set_error("attention_rows_mma: rows of %d elements need more shared memory than a block has", p.row_width);
     return DK_ERR_ARG;
@@ -269,7 +290,7 @@ int launch(const DkRowAttnParams& p, int m_tiles, int splits, float* part, cudaS
   static size_t configured_on[DK_MAX_DEVICES] = {0};
   size_t& configured = configured_on[dk_current_device()];
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_rows_mma_kernel<WARPS, KT, DVMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_rows_mma_kernel<WARPS, KT, DVMAX, RM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
       dk_set_error("attention_rows_mma: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
       return DK_ERR_LAUNCH;
@@ -277,7 +298,7 @@ int launch(const DkRowAttnParams& p, int m_tiles, int splits, float* part, cudaS
     configured = smem;
   }
   dim3 grid(m_tiles, splits, p.rows * p.KV);
-  attention_rows_mma_kernel<WARPS, KT, DVMAX><<<grid, WARPS * 32, smem, stream>>>(p, part);
+  attention_rows_mma_kernel<WARPS, KT, DVMAX, RM><<<grid, WARPS * 32, smem, stream>>>(p, part);
   return dk_check_launch("attention_rows_mma");
 }
 }  // namespace
@@ -288,7 +309,7 @@ extern "C" int dk_attention_rows_mma_supported(const DkRowAttnParams* pp) {
   if (p.dk % 16 || p.dv % 16 || p.dk < 16 || p.dv < 16 || p.dv > 256) return 0;
   if (p.row_width % 8 || p.k_off % 8 || p.v_off % 8 || p.q_stride % 8 || p.q_head_stride % 8) return 0;
   if (p.ps < 1 || p.ps > 128 || (p.ps & (p.ps - 1)) != 0) return 0;
-  if ((size_t)64 * pad128(p.dk * 2) + (size_t)PSTAGES * 64 * pad128(p.row_width * 2) > 220 * 1024) return 0;
+  if ((size_t)128 * pad128(p.dk * 2) + (size_t)PSTAGES * 64 * pad128(p.row_width * 2) > 220 * 1024) return 0;
   return 1;
 }
 
@@ -308,12 +329,18 @@ extern "C" int dk_attention_rows_mma(const DkRowAttnParams* pp, int max_m, int s
   DK_REQUIRE(p.row_q_start && p.row_q_len && p.row_pos_start && p.tok_row, "attention_rows_mma: the rows' arrays are missing");
   DK_REQUIRE((long long)p.rows * p.KV <= 65535, "attention_rows_mma: grid too large");
   int e;
-  const bool small = max_m <= 16;
-#define GO(DVMAX) (small ? launch<1, 32, DVMAX>(p, 1, splits, part, stream) : launch<4, 64, DVMAX>(p, (max_m + 63) / 64, splits, part, stream))
-  if (p.dv <= 64) e = GO(64);
-  else if (p.dv <= 128) e = GO(128);
-  else e = GO(256);
-#undef GO
+  // a single token's heads: one warp; up to 64 query rows or a wide value: 16 rows a warp; else 32 rows a warp
+  if (max_m <= 16) {
+    if (p.dv <= 64) e = launch<1, 32, 64, 1>(p, max_m, splits, part, stream);
+    else if (p.dv <= 128) e = launch<1, 32, 128, 1>(p, max_m, splits, part, stream);
+    else e = launch<1, 32, 256, 1>(p, max_m, splits, part, stream);
+  } else if (p.dv > 128) {
+    e = launch<4, 64, 256, 1>(p, max_m, splits, part, stream);
+  } else if (max_m <= 64) {
+    e = p.dv <= 64 ? launch<4, 64, 64, 1>(p, max_m, splits, part, stream) : launch<4, 64, 128, 1>(p, max_m, splits, part, stream);
+  } else {
+    e = p.dv <= 64 ? launch<4, 64, 64, 2>(p, max_m, splits, part, stream) : launch<4, 64, 128, 2>(p, max_m, splits, part, stream);
+  }
   if (e != 0 || splits == 1) return e;
   DK_REQUIRE(p.H <= 65535, "attention_rows_mma: too many heads");
   attention_rows_merge_kernel<<<dim3(p.T, p.H), 128, 0, stream>>>(p, part, splits);

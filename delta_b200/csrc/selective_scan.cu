@@ -63,14 +63,22 @@ __global__ void conv_state_kernel(const T* __restrict__ xin, int in_stride, floa
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 // Block: 128 threads = (128 / P) channels x P lanes; lane p of a channel keeps the states n = p, p + P, ...
-// grid (ceil(C / (128 / P)), rows).  Tokens of the row go through shared memory TT at a time.
+// grid (ceil(C / (128 / P)), rows * segs).  Tokens go through shared memory TT at a time.
+//
+// A long row is cut into segments of `seg_len` tokens that run in parallel (MODE 1, 2); the recurrence is linear, so
+//   MODE 1  runs every segment from a zero state and keeps its end state E_g and the sum of its step sizes d_g;
+//   combine walks the segments of a row in order: start_0 = the request's state, start_{g+1} = exp(A d_g) start_g + E_g
+//           (the decays of a segment multiply to exp(A * sum of dt)), and the last value is the request's new state;
+//   MODE 2  runs every segment again from its start state and writes y.
+// MODE 0 is the whole row in one block, from and into the request's state (single tokens, short portions).
 constexpr int TT = 16;
-template <typename T, int P, int MAXS>
+template <typename T, int P, int MAXS, int MODE>
 __global__ void __launch_bounds__(128) selective_scan_kernel(
     const T* __restrict__ x, const T* __restrict__ dtraw, const T* __restrict__ bc, int bc_stride, int b_off, int c_off,
     const T* __restrict__ z, int z_stride, const float* __restrict__ A_log, const float* __restrict__ Dw,
     const float* __restrict__ dt_bias, float* __restrict__ scan_state, T* __restrict__ out, const int* __restrict__ row_slot,
-    const int* __restrict__ row_q_start, const int* __restrict__ row_q_len, int C, int N) {
+    const int* __restrict__ row_q_start, const int* __restrict__ row_q_len, int C, int N, int segs, int seg_len,
+    float* __restrict__ seg_state, float* __restrict__ seg_dt) {
   constexpr int CH = 128 / P;
   extern __shared__ float sm[];
   float* s_dt = sm;                 // [TT][CH]
@@ -79,22 +87,27 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
   float* s_y = s_g + TT * CH;       // [TT][CH]
   float* s_B = s_y + TT * CH;       // [TT][N]
   float* s_C = s_B + TT * N;        // [TT][N]
-  const int row = blockIdx.y;
+  const int row = blockIdx.y / segs, seg = blockIdx.y % segs;
   const int c0 = blockIdx.x * CH;
   const int cl = threadIdx.x / P, part = threadIdx.x % P;
   const int c = c0 + cl;
   const bool live = c < C;
-  const int q0 = row_q_start[row], L = row_q_len[row];
-  float* st = scan_state + ((size_t)row_slot[row] * C + (live ? c : 0)) * N;
+  const int row_len = row_q_len[row];
+  if (seg * seg_len >= row_len) return;
+  const int q0 = row_q_start[row] + seg * seg_len;
+  const int L = MODE == 0 ? row_len : min(seg_len, row_len - seg * seg_len);
+  float* st = MODE == 0 ? scan_state + ((size_t)row_slot[row] * C + (live ? c : 0)) * N
+                        : seg_state + ((size_t)blockIdx.y * C + (live ? c : 0)) * N;
   float s[MAXS], a[MAXS];
 #pragma unroll
   for (int k = 0; k < MAXS; ++k) {
     const int n = part + k * P;
     const bool on = live && n < N;
-    s[k] = on ? st[n] : 0.f;
+    s[k] = (on && MODE != 1) ? st[n] : 0.f;
     a[k] = on ? -expf(A_log[(size_t)c * N + n]) : 0.f;
   }
   const float dsk = live ? Dw[c] : 0.f;
+  float dt_sum = 0.f;
   for (int t0 = 0; t0 < L; t0 += TT) {
     const int nt = min(TT, L - t0);
     __syncthreads();
@@ -105,8 +118,10 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
       if (c0 + cc < C) {
         dtv = softplus_f(to_f32<T>(dtraw[tok * C + c0 + cc]) + dt_bias[c0 + cc]);
         xv = to_f32<T>(x[tok * C + c0 + cc]);
-        const float zv = to_f32<T>(z[tok * z_stride + c0 + cc]);
-        gv = zv / (1.f + expf(-zv));
+        if (MODE != 1) {
+          const float zv = to_f32<T>(z[tok * z_stride + c0 + cc]);
+          gv = zv / (1.f + expf(-zv));
+        }
       }
       s_dt[idx] = dtv;
       s_x[idx] = xv;
@@ -116,38 +131,65 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
       const int tt = idx / N, n = idx % N;
       const size_t tok = (size_t)(q0 + t0 + tt);
       s_B[idx] = to_f32<T>(bc[tok * bc_stride + b_off + n]);
-      s_C[idx] = to_f32<T>(bc[tok * bc_stride + c_off + n]);
+      if (MODE != 1) s_C[idx] = to_f32<T>(bc[tok * bc_stride + c_off + n]);
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
       const float dtv = s_dt[tt * CH + cl], xv = s_x[tt * CH + cl];
       const float dx = dtv * xv;
+      dt_sum += dtv;
       float acc = 0.f;
 #pragma unroll
       for (int k = 0; k < MAXS; ++k) {
         const int n = part + k * P;
         if (n < N) {
           s[k] = fmaf(expf(dtv * a[k]), s[k], dx * s_B[tt * N + n]);
-          acc = fmaf(s[k], s_C[tt * N + n], acc);
+          if (MODE != 1) acc = fmaf(s[k], s_C[tt * N + n], acc);
         }
       }
+      if (MODE != 1) {
 #pragma unroll
-      for (int o = P / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (part == 0) s_y[tt * CH + cl] = (acc + dsk * xv) * s_g[tt * CH + cl];
+        for (int o = P / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (part == 0) s_y[tt * CH + cl] = (acc + dsk * xv) * s_g[tt * CH + cl];
+      }
     }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * CH; idx += 128) {
-      const int tt = idx / CH, cc = idx % CH;
-      if (c0 + cc < C) out[(size_t)(q0 + t0 + tt) * C + c0 + cc] = from_f32<T>(s_y[idx]);
+    if (MODE != 1) {
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < nt * CH; idx += 128) {
+        const int tt = idx / CH, cc = idx % CH;
+        if (c0 + cc < C) out[(size_t)(q0 + t0 + tt) * C + c0 + cc] = from_f32<T>(s_y[idx]);
+      }
     }
   }
-  if (live) {
+  if (live && MODE != 2) {
 #pragma unroll
     for (int k = 0; k < MAXS; ++k) {
       const int n = part + k * P;
       if (n < N) st[n] = s[k];
     }
+    if (MODE == 1 && part == 0) seg_dt[(size_t)blockIdx.y * C + c] = dt_sum;
   }
+}
+
+// grid (ceil(C * N / 256), rows): thread (c, n) turns the segments' end states into their start states, in order
+__global__ void scan_combine_kernel(const float* __restrict__ A_log, float* __restrict__ scan_state, float* __restrict__ seg_state,
+                                    const float* __restrict__ seg_dt, const int* __restrict__ row_slot,
+                                    const int* __restrict__ row_q_len, int C, int N, int segs, int seg_len) {
+  const int row = blockIdx.y;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)C * N) return;
+  const int c = (int)(i / N);
+  const int used = (row_q_len[row] + seg_len - 1) / seg_len;
+  float* slot = scan_state + (size_t)row_slot[row] * C * N + i;
+  const float a = -expf(A_log[i]);
+  float s = *slot;
+  for (int g = 0; g < used && g < segs; ++g) {
+    float* e = seg_state + ((size_t)(row * segs + g) * C) * N + i;
+    const float end = *e;
+    *e = s;
+    s = fmaf(expf(a * seg_dt[(size_t)(row * segs + g) * C + c]), s, end);
+  }
+  *slot = s;
 }
 }  // namespace
 
@@ -176,31 +218,50 @@ extern "C" int dk_conv_silu(const void* xin, int in_stride, const float* w, cons
   return dk_check_launch("conv_silu");
 }
 
+// seg_len > 0: rows longer than seg_len tokens are cut into segments that run in parallel (`segs` = the most segments of
+// any row); seg_state holds rows * segs * C * N floats and seg_dt rows * segs * C.  seg_len == 0: every row in one block.
 extern "C" int dk_selective_scan(const void* x, const void* dtraw, const void* bc, int bc_stride, int b_off, int c_off,
                                  const void* z, int z_stride, const float* A_log, const float* Dw, const float* dt_bias,
                                  float* scan_state, void* out, const int* row_slot, const int* row_q_start,
-                                 const int* row_q_len, int rows, int C, int N, int dtype, cudaStream_t stream) {
+                                 const int* row_q_len, int rows, int C, int N, int dtype, int segs, int seg_len, float* seg_state,
+                                 float* seg_dt, cudaStream_t stream) {
   if (rows == 0) return 0;
   DK_REQUIRE(rows > 0 && C > 0 && N > 0, "selective_scan: bad sizes rows=%d C=%d N=%d", rows, C, N);
   DK_REQUIRE(N <= 256, "selective_scan: %d states per channel; this kernel takes up to 256", N);
-  DK_REQUIRE(rows <= 65535, "selective_scan: too many rows");
   DK_REQUIRE(dtype == DK_F32 || dtype == DK_BF16, "selective_scan: unknown dtype %d", dtype);
-#define LAUNCH(T, P)                                                                                                          \
+  const bool cut = seg_len > 0;
+  DK_REQUIRE(!cut || (segs >= 1 && seg_len % TT == 0 && seg_state != nullptr && seg_dt != nullptr),
+             "selective_scan: segments of %d tokens (a multiple of %d) need their buffers", seg_len, TT);
+  if (!cut) segs = 1;
+  DK_REQUIRE((long long)rows * segs <= 65535, "selective_scan: too many rows or segments");
+#define LAUNCH(T, P, MODE)                                                                                                    \
   do {                                                                                                                        \
     constexpr int CH = 128 / P;                                                                                               \
     const size_t smem = (size_t)(4 * TT * CH + 2 * TT * N) * sizeof(float);                                                  \
-    selective_scan_kernel<T, P, 8><<<dim3((C + CH - 1) / CH, rows), 128, smem, stream>>>(                                     \
+    selective_scan_kernel<T, P, 8, MODE><<<dim3((C + CH - 1) / CH, rows * segs), 128, smem, stream>>>(                        \
         (const T*)x, (const T*)dtraw, (const T*)bc, bc_stride, b_off, c_off, (const T*)z, z_stride, A_log, Dw, dt_bias,      \
-        scan_state, (T*)out, row_slot, row_q_start, row_q_len, C, N);                                                        \
+        scan_state, (T*)out, row_slot, row_q_start, row_q_len, C, N, segs, cut ? seg_len : (1 << 30), seg_state, seg_dt);    \
   } while (0)
-#define PICK(T)                       \
-  do {                                \
-    if (N <= 32) LAUNCH(T, 4);        \
-    else if (N <= 64) LAUNCH(T, 8);   \
-    else LAUNCH(T, 32);               \
+#define PICK(T, MODE)                       \
+  do {                                      \
+    if (N <= 32) LAUNCH(T, 4, MODE);        \
+    else if (N <= 64) LAUNCH(T, 8, MODE);   \
+    else LAUNCH(T, 32, MODE);               \
   } while (0)
-  if (dtype == DK_F32) PICK(float);
-  else PICK(__nv_bfloat16);
+#define BOTH(MODE)                          \
+  do {                                      \
+    if (dtype == DK_F32) PICK(float, MODE); \
+    else PICK(__nv_bfloat16, MODE);         \
+  } while (0)
+  if (!cut) {
+    BOTH(0);
+    return dk_check_launch("selective_scan");
+  }
+  BOTH(1);
+  scan_combine_kernel<<<dim3((unsigned)(((size_t)C * N + 255) / 256), rows), 256, 0, stream>>>(A_log, scan_state, seg_state, seg_dt,
+                                                                                              row_slot, row_q_len, C, N, segs, seg_len);
+  BOTH(2);
+#undef BOTH
 #undef PICK
 #undef LAUNCH
   return dk_check_launch("selective_scan");

@@ -40,7 +40,7 @@ template <typename T, typename TO>
 __global__ void stream_norm_kernel(float* __restrict__ X, const T* __restrict__ y, const float* __restrict__ mix,
                                    const float* __restrict__ outw, const float* __restrict__ inw, const float* __restrict__ w,
                                    TO* __restrict__ out, const int* __restrict__ rows, int S, int d, float eps, int write_back) {
-  extern __shared__ float usm[];   // d floats + 33
+  extern __shared__ __align__(16) float usm[];   // d floats + 33
   float* scratch = usm + d;
   __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_out[MAX_STREAMS], s_in[MAX_STREAMS];
   const int r = blockIdx.x;
@@ -96,6 +96,99 @@ __global__ void stream_norm_kernel(float* __restrict__ X, const T* __restrict__ 
   for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TO>(usm[i] * inv * w[i]);
 }
 
+// The same for a width that is a multiple of 4 and a compile-time number of copies: 16-byte loads and stores, all
+// copies of four neighbouring entries in registers at once.
+template <typename T>
+__device__ __forceinline__ float4 load4(const T* p);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&a);
+  raw.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename T, typename TO, int S>
+__global__ void stream_norm_vec_kernel(float* __restrict__ X, const T* __restrict__ y, const float* __restrict__ mix,
+                                       const float* __restrict__ outw, const float* __restrict__ inw, const float* __restrict__ w,
+                                       TO* __restrict__ out, const int* __restrict__ rows, int d, float eps, int write_back) {
+  extern __shared__ __align__(16) float usm[];   // d floats + 33
+  float* scratch = usm + d;
+  const int r = blockIdx.x;
+  const int tk = rows ? rows[r] : r;
+  float c_mix[S][S], c_out[S], c_in[S];
+#pragma unroll
+  for (int s = 0; s < S; ++s) {
+    c_out[s] = outw ? outw[s] : 0.f;
+    c_in[s] = inw ? inw[s] : 1.f;
+#pragma unroll
+    for (int t2 = 0; t2 < S; ++t2) c_mix[s][t2] = mix ? mix[s * S + t2] : 0.f;
+  }
+  float* xs = X + (size_t)tk * S * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+    float4 v[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) v[s] = *reinterpret_cast<const float4*>(xs + (size_t)s * d + i);
+    if (y != nullptr) {
+      const float4 yv = load4<T>(y + (size_t)tk * d + i);
+      float4 n[S];
+#pragma unroll
+      for (int t2 = 0; t2 < S; ++t2) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+          a.x = fmaf(c_mix[s][t2], v[s].x, a.x);
+          a.y = fmaf(c_mix[s][t2], v[s].y, a.y);
+          a.z = fmaf(c_mix[s][t2], v[s].z, a.z);
+          a.w = fmaf(c_mix[s][t2], v[s].w, a.w);
+        }
+        n[t2] = make_float4(fmaf(c_out[t2], yv.x, a.x), fmaf(c_out[t2], yv.y, a.y), fmaf(c_out[t2], yv.z, a.z), fmaf(c_out[t2], yv.w, a.w));
+      }
+#pragma unroll
+      for (int s = 0; s < S; ++s) {
+        v[s] = n[s];
+        if (write_back) *reinterpret_cast<float4*>(xs + (size_t)s * d + i) = n[s];
+      }
+    }
+    float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      u.x = fmaf(c_in[s], v[s].x, u.x);
+      u.y = fmaf(c_in[s], v[s].y, u.y);
+      u.z = fmaf(c_in[s], v[s].z, u.z);
+      u.w = fmaf(c_in[s], v[s].w, u.w);
+    }
+    *reinterpret_cast<float4*>(usm + i) = u;
+    ss += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+  }
+  if (out == nullptr) return;
+  TO* o = out + (size_t)r * d;
+  float inv = 1.f;
+  if (w != nullptr) {
+    ss = block_sum(ss, scratch);
+    inv = 1.f / sqrtf(ss / (float)d + eps);
+  }
+  for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+    const float4 u = *reinterpret_cast<const float4*>(usm + i);
+    const float4 wv = w != nullptr ? *reinterpret_cast<const float4*>(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+    store4<TO>(o + i, make_float4(u.x * inv * wv.x, u.y * inv * wv.y, u.z * inv * wv.z, u.w * inv * wv.w));
+  }
+}
+
 // kind 0: relu(x)^2; 1: gelu with the tanh form; 2: silu.  Computed in float, rounded once.
 template <typename T>
 __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, int kind) {
@@ -148,16 +241,27 @@ extern "C" int dk_stream_norm(float* X, const void* y, const float* mix, const f
   DK_REQUIRE(S >= 1 && S <= MAX_STREAMS, "stream_norm: %d copies of the stream; this kernel takes 1 to %d", S, MAX_STREAMS);
   DK_REQUIRE(d <= 12000, "stream_norm: width %d is above the 12000 this kernel keeps in shared memory", d);
   DK_REQUIRE(y == nullptr || (mix != nullptr && outw != nullptr), "stream_norm: an update is given without its weights");
-  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-  const size_t smem = (size_t)(d + 33) * sizeof(float);
-#define LAUNCH(T, TO)                                                                                                          \
-  stream_norm_kernel<T, TO><<<n_rows, threads, smem, stream>>>(X, (const T*)y, mix, outw, inw, w, (TO*)out, rows, S, d, eps, \
-                                                               write_back)
+  const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
+  const size_t smem = (size_t)(d + 36) * sizeof(float);
+  const bool vec = (d % 4) == 0 && (S == 1 || S == 2 || S == 4) && ((uintptr_t)X % 16) == 0 && ((uintptr_t)y % 8) == 0 &&
+                   ((uintptr_t)out % 8) == 0 && ((uintptr_t)w % 16) == 0;
+#define VEC(T, TO, SS) \
+  stream_norm_vec_kernel<T, TO, SS><<<n_rows, threads, smem, stream>>>(X, (const T*)y, mix, outw, inw, w, (TO*)out, rows, d, eps, write_back)
+#define LAUNCH(T, TO)                                                                                                            \
+  do {                                                                                                                           \
+    if (vec && S == 1) VEC(T, TO, 1);                                                                                            \
+    else if (vec && S == 2) VEC(T, TO, 2);                                                                                       \
+    else if (vec && S == 4) VEC(T, TO, 4);                                                                                       \
+    else                                                                                                                         \
+      stream_norm_kernel<T, TO><<<n_rows, threads, smem, stream>>>(X, (const T*)y, mix, outw, inw, w, (TO*)out, rows, S, d, eps, \
+                                                                   write_back);                                                  \
+  } while (0)
   if (y_dtype == DK_F32 && out_dtype == DK_F32) LAUNCH(float, float);
   else if (y_dtype == DK_BF16 && out_dtype == DK_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (y_dtype == DK_BF16 && out_dtype == DK_F32) LAUNCH(__nv_bfloat16, float);
   else DK_REQUIRE(false, "stream_norm: unsupported dtypes y=%d out=%d", y_dtype, out_dtype);
 #undef LAUNCH
+#undef VEC
   return dk_check_launch("stream_norm");
 }
 

@@ -55,7 +55,7 @@ _SIGNATURES = {
     "dk_activation": [P, P, L, I, I, P],
     "dk_softcap": [P, L, F, P],
     "dk_conv_silu": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
-    "dk_selective_scan": [P, P, P, I, I, I, P, I, P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "dk_selective_scan": [P, P, P, I, I, I, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P, P],
     "dk_attention_rows_plain": [C.POINTER(RowAttnParams), P],
     "dk_rows_append": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
     "dk_latent_prepare": [P, I, P, P, P, I, P, I, P, I, I, I, P, F, P, I, I, I, I, I, I, I, P, P],
@@ -135,11 +135,47 @@ def declare(name: str, argtypes: list) -> None:
 
 
 LAUNCHES = [0]
+PROFILE = None      # a list while launches are being timed: (name of the launcher, event recorded behind it)
+
+
+def profile_start() -> None:
+    """From now on an event is recorded behind every launcher (and every library product that is counted), so that the
+    device time between two of them can be read afterwards with ``profile_stop``.  For measurements only: nothing is
+    synchronised, but a recorded step cannot be captured into a graph meanwhile."""
+    global PROFILE
+    import torch
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    PROFILE = [("start", ev)]
+
+
+def profile_mark(what: str) -> None:
+    if PROFILE is not None:
+        import torch
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        PROFILE.append((what, ev))
+
+
+def profile_stop() -> dict:
+    """Stops timing and returns {launcher: (calls, milliseconds)}: the device time from the end of the launcher before
+    to the end of this one, summed over its calls (launch gaps included; waits for the device)."""
+    global PROFILE
+    import torch
+    marks, PROFILE = PROFILE or [], None
+    torch.cuda.synchronize()
+    out = {}
+    for (_, e0), (what, e1) in zip(marks, marks[1:]):
+        n, ms = out.get(what, (0, 0.0))
+        out[what] = (n + 1, ms + e0.elapsed_time(e1))
+    return out
 
 
 def check(code: int, what: str, kernels: int = 1) -> None:
     """Raises when a launcher returned an error; counts the kernels it launched."""
     LAUNCHES[0] += kernels
+    if PROFILE is not None:
+        profile_mark(what)
     if code != 0:
         msg = load().dk_last_error().decode("utf-8", "replace")
         raise KernelError(f"{what}: {msg} (code {code})")

@@ -64,6 +64,15 @@ def count_launch(n: int = 1) -> None:
     _l.LAUNCHES[0] += n
 
 
+def count_library(what: str = "library product") -> None:
+    """To be called behind a library kernel on the hot path: counts it and, while launches are timed, marks it."""
+    if _l.PROFILE is not None:
+        _l.profile_mark(what)
+
+
+profile_start, profile_stop = _l.profile_start, _l.profile_stop
+
+
 def new_error_record(device) -> torch.Tensor:
     """Four ints the kernels write {code, a, b, c} into when they meet a bad index."""
     return torch.zeros(4, dtype=torch.int32, device=device)
@@ -476,10 +485,13 @@ def conv_silu(xin, in_stride, weight, bias, conv_state, out, *, tok_row, row_slo
 
 
 def selective_scan(x, dtraw, bc, b_off, c_off, z, z_stride, A_log, D, dt_bias, scan_state, out, *, row_slot, row_q_start,
-                   row_q_len):
+                   row_q_len, seg_len=0, segs=1, seg_state=None, seg_dt=None):
     """The recurrence of the selective state-space mixer over each row's tokens, from and into ``scan_state``
     [slots, C, N] (float32).  ``bc`` [T, stride] holds a token's input map at ``b_off`` and output map at ``c_off``
-    (N each); ``z`` points at the gate's C values in rows of ``z_stride`` elements."""
+    (N each); ``z`` points at the gate's C values in rows of ``z_stride`` elements.  ``seg_len`` > 0: rows are cut into
+    segments of that many tokens which run in parallel (three kernels: every segment from zero, the segments' start states
+    in order, every segment again from its start); ``segs`` is the most segments of any row, ``seg_state``
+    [rows * segs, C, N] and ``seg_dt`` [rows * segs, C] (float32) are working memory."""
     T, C_ = x.shape
     N = A_log.shape[1]
     i32, f32 = torch.int32, torch.float32
@@ -487,7 +499,8 @@ def selective_scan(x, dtraw, bc, b_off, c_off, z, z_stride, A_log, D, dt_bias, s
         _ptr(x, "x"), _ptr(dtraw, "dtraw", x.dtype), _ptr(bc, "bc", x.dtype), bc.shape[1], int(b_off), int(c_off), z, int(z_stride),
         _ptr(A_log, "A_log", f32), _ptr(D, "D", f32), _ptr(dt_bias, "dt_bias", f32), _ptr(scan_state, "scan_state", f32),
         _ptr(out, "out", x.dtype), _ptr(row_slot, "row_slot", i32), _ptr(row_q_start, "row_q_start", i32),
-        _ptr(row_q_len, "row_q_len", i32), row_slot.shape[0], C_, N, dtype_code(x.dtype), _stream()), "selective_scan")
+        _ptr(row_q_len, "row_q_len", i32), row_slot.shape[0], C_, N, dtype_code(x.dtype), int(segs), int(seg_len),
+        _ptr(seg_state, "seg_state", f32), _ptr(seg_dt, "seg_dt", f32), _stream()), "selective_scan", 3 if seg_len else 1)
     return out
 
 

@@ -26,7 +26,7 @@ from . import linear, row_attention
 from .base import MIXERS, PAGE, POSITION_ENCODINGS, CacheSpec, Mixer, PartSpec, TensorSpec
 
 
-LIBRARY_BATCHED = False     # bfloat16 prompt portions: the library's batched product on strided views
+LIBRARY_BATCHED = True      # bfloat16 prompt portions: the library's batched product on strided views
 
 
 def heads_product(ctx, a, a_off, lda, sa, w, n, k, c, c_off, ldc, sc, heads):
@@ -43,6 +43,7 @@ def heads_product(ctx, a, a_off, lda, sa, w, n, k, c, c_off, ldc, sc, heads):
         av = torch.as_strided(a, (heads, T, k), (sa, lda, 1), a.storage_offset() + a_off)
         cv = torch.as_strided(c, (heads, T, n), (sc, ldc, 1), c.storage_offset() + c_off)
         torch.bmm(av, w.transpose(1, 2), out=cv)
+        ops.count_library("library batched product")
         return
     ops.gemm_nt_plain_batched(a.data_ptr() + a_off * es, w.data_ptr(), c.data_ptr() + c_off * es, T, n, k, lda, k, ldc, heads,
                               sa, n * k, sc, a.dtype, c.dtype)

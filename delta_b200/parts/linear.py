@@ -92,8 +92,11 @@ def _run(kind: str, x, w, out, swiglu: bool, err=None):
     ops.count_launch()
     if swiglu:
         gu = torch.mm(x, w.t())
+        ops.count_library()
         return ops.silu_mul(gu, out)
-    return torch.mm(x, w.t(), out=out)
+    r = torch.mm(x, w.t(), out=out)
+    ops.count_library()
+    return r
 
 
 def _time(fn, reps: int = 12) -> float:
@@ -223,7 +226,9 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tenso
             return out
     if out_dtype == x.dtype:
         ops.count_launch()
-        return torch.mm(x, w.t())
+        r = torch.mm(x, w.t())
+        ops.count_library()
+        return r
     out = torch.empty((T, N), dtype=out_dtype, device=x.device)
     if T:
         ops.gemm_nt_plain(x, w, out)

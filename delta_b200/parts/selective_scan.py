@@ -20,6 +20,7 @@ from ..kernels import ops
 from . import linear
 from .base import MIXERS, Mixer, StateSpec, TensorSpec
 
+SEGMENT = 128           # tokens of a segment when a long portion's recurrence is run in parallel pieces
 CONV_STATE = "conv"
 SCAN_STATE = "scan"
 
@@ -65,6 +66,13 @@ class SelectiveScan(Mixer):
         low = linear.linear(ctx, xc, self.w_x)                                  # [T, r + 2N]: dt | B | C
         dtraw = linear.linear(ctx, low[:, :r].contiguous(), self.w_dt)          # [T, C], before the bias and softplus
         y = torch.empty((T, C), dtype=x.dtype, device=x.device)
+        seg = {}
+        if not ctx.replayable and ctx.max_q_len > SEGMENT:
+            # long portions: the recurrence is linear, so segments of a row run in parallel and are stitched together
+            segs = -(-ctx.max_q_len // SEGMENT)
+            n = ctx.num_rows * segs
+            seg = dict(seg_len=SEGMENT, segs=segs, seg_state=ctx.scratch("selective_scan.segments", (n, C, N), torch.float32),
+                       seg_dt=ctx.scratch("selective_scan.segment_dt", (n, C), torch.float32))
         ops.selective_scan(xc, dtraw, low, r, r + N, xz.data_ptr() + C * xz.element_size(), 2 * C, self.A_log, self.D, self.dt_b,
-                           cache.state[SCAN_STATE], y, **rows)
+                           cache.state[SCAN_STATE], y, **rows, **seg)
         return linear.linear(ctx, y, self.w_o)
