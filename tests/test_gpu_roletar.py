@@ -227,3 +227,20 @@ def test_trace_replay_command(tmp_path_factory, tmp_path):
     for k in range(3):
         assert got[k].shape == want[k].shape
         assert (got[k] - want[k]).abs().max().item() <= TOL["float32"] * want[k].abs().max().item()
+
+
+def test_command_line_generates(tmp_path_factory, tmp_path):
+    """``python -m delta_b200.cli`` on a Roletar folder: the model class comes from config.json, prompts are scheduled and sampled."""
+    import random
+    from delta_b200 import cli
+    cfg, W, folder = model(tmp_path_factory, "plain")
+    out = tmp_path / "result.json"
+    rc = cli.main(["--model", str(folder), "--B", "3", "--max_len", "128", "--dataset", "random", "--prompt_len", "19", "--num_samples", "5",
+                   "--max_new_tokens", "6", "--dtype", "float32", "--max_tokens_per_step", "32", "--out", str(out)])
+    assert rc == 0
+    res = json.loads(out.read_text())
+    assert res["summary"]["requests"] == 5 and res["summary"]["generated_tokens"] == 30
+    rng = random.Random(123)       # the command line's default seed draws the prompts
+    prompt = [rng.randrange(cfg["vocab"]) for _ in range(19)]
+    first = [r for r in res["results"] if r["request_id"] == 0][0]
+    assert first["output_ids"] == greedy_plain(cfg, W, prompt, 6)
