@@ -46,6 +46,12 @@ Other workloads (``--workload``), each printing one JSON line of the same shape:
                during decoding, a page at a time in turns with the other requests; the last sixth of
                the decode steps, with the pool handing pages out in runs and one by one
 
+  roletar      the Roletar design (32-bit mixed residual streams, selective scan, latent attention, windowed
+               attention with sinks; random weights at widths ``--width``, layers of real sizes) beside the Yi
+               architecture at the same width and number of layer runs: prefill of one 2,048-token prompt and
+               decode at batch 8, context 2,048, through ``ModelRunner.step``; then every launcher's share of
+               one such step with the fraction of the peaks that the elementwise and attention kernels reach
+
 ``--impl reference`` runs the unmodified hoenza/DELTA engine (baseline/reference_arm.py) on the
 default workload and prints its line.
 """
