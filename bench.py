@@ -434,7 +434,7 @@ def roletar_workload(args) -> int:
 
     def measure(cfg_json, vocab):
         ec = EngineConfig(max_batch=B + 1, max_seq_len=CTX + 64, page_size=16, dtype="bfloat16", max_tokens_per_step=T,
-                          num_pages=(B + 1) * (CTX + 64) // 16)
+                          num_pages=(B + 1) * (CTX + 64) // 16, cuda_graph_decode=True)
         r = ModelRunner(config_json=cfg_json, seed=0, engine_config=ec)
         prompt = torch.randint(0, vocab, (T,), generator=gen).tolist()
         res = {}
@@ -464,10 +464,18 @@ def roletar_workload(args) -> int:
         ops.profile_start()
         decode()
         res["decode_launchers"] = ops.profile_stop()
-        res["launches_per_decode_step"] = None
         l0 = ops.launch_count()
         decode()
         res["launches_per_decode_step"] = ops.launch_count() - l0
+        # the same step replayed from a recorded CUDA graph with sampling, as generation runs it
+        for s in slots:
+            r.cache.grow(s, pos[0] + 1)
+
+        def decode_graph():
+            r.step_and_sample([RowInput(s, [7], pos[0], [0]) for s in slots])
+        for _ in range(4):
+            decode_graph()
+        res["decode_graph_ms"] = timed(decode_graph, max(3, args.steps // 8)) if r.decode_graph_ready(B) else None
         del r
         torch.cuda.empty_cache()
         return res
@@ -515,11 +523,11 @@ def roletar_workload(args) -> int:
             return rows
         out["sizes"][str(d)] = {
             "roletar": {"prefill_tok_s": T / a["prefill_ms"] * 1e3, "prefill_ms": a["prefill_ms"], "decode_tok_s": B / a["decode_ms"] * 1e3,
-                        "decode_ms": a["decode_ms"], "launches_per_decode_step": a["launches_per_decode_step"],
+                        "decode_ms": a["decode_ms"], "decode_graph_ms": a["decode_graph_ms"], "launches_per_decode_step": a["launches_per_decode_step"],
                         "prefill_launchers": fractions(a["prefill_launchers"], work),
                         "decode_launchers": fractions(a["decode_launchers"], {})},
             "yi": {"prefill_tok_s": T / b["prefill_ms"] * 1e3, "prefill_ms": b["prefill_ms"], "decode_tok_s": B / b["decode_ms"] * 1e3,
-                   "decode_ms": b["decode_ms"], "launches_per_decode_step": b["launches_per_decode_step"],
+                   "decode_ms": b["decode_ms"], "decode_graph_ms": b["decode_graph_ms"], "launches_per_decode_step": b["launches_per_decode_step"],
                    "prefill_launchers": fractions(b["prefill_launchers"], yi_work),
                    "decode_launchers": fractions(b["decode_launchers"], {})},
             "config": {"width": d, "layer_runs": runs, "prefill_tokens": T, "decode_batch": B, "decode_context": CTX,
