@@ -8,7 +8,8 @@
 // tiles (cp.async, two stages, 16-byte chunks swizzled for ldmatrix); a cached row holds key and value, so one
 // copy brings both, and a value that is the front of its key is not copied twice.  Per tile and warp:
 // S = Q K^T (mma.sync.m16n8k16, float accumulators), mask by position (causal, window), online softmax in
-// float, O += P V.  The sink joins the denominator when the result is finished.
+// float, O += P V with P split into two bfloat16 parts (so the softmax weights keep 16 bits of mantissa; their sum
+// is taken in float from the unrounded weights).  The sink joins the denominator when the result is finished.
 //
 // grid (tiles of query rows, splits, batch rows * KV).  With more than one split each block takes a share of the
 // key tiles and stores (unnormalised O, running maximum, sum) per query row; a second kernel merges them.
@@ -139,7 +140,6 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
           }
         }
       }
-      uint32_t pa[RM][KT / 16][4];
 #pragma unroll
       for (int rm = 0; rm < RM; ++rm) {
         float tmax[2] = {-INFINITY, -INFINITY};
@@ -175,22 +175,33 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
           o[rm][n][2] *= corr[1];
           o[rm][n][3] *= corr[1];
         }
+        // the weights, in float, take the scores' place
 #pragma unroll
-        for (int kb2 = 0; kb2 < KT / 16; ++kb2) {
-          const float p00 = exp2f(s[rm][2 * kb2][0] - m_use[0]), p01 = exp2f(s[rm][2 * kb2][1] - m_use[0]);
-          const float p02 = exp2f(s[rm][2 * kb2][2] - m_use[1]), p03 = exp2f(s[rm][2 * kb2][3] - m_use[1]);
-          const float p10 = exp2f(s[rm][2 * kb2 + 1][0] - m_use[0]), p11 = exp2f(s[rm][2 * kb2 + 1][1] - m_use[0]);
-          const float p12 = exp2f(s[rm][2 * kb2 + 1][2] - m_use[1]), p13 = exp2f(s[rm][2 * kb2 + 1][3] - m_use[1]);
-          l_run[rm][0] += p00 + p01 + p10 + p11;
-          l_run[rm][1] += p02 + p03 + p12 + p13;
-          pa[rm][kb2][0] = pack_bf16(p00, p01);
-          pa[rm][kb2][1] = pack_bf16(p02, p03);
-          pa[rm][kb2][2] = pack_bf16(p10, p11);
-          pa[rm][kb2][3] = pack_bf16(p12, p13);
+        for (int j = 0; j < KT / 8; ++j) {
+          s[rm][j][0] = exp2f(s[rm][j][0] - m_use[0]);
+          s[rm][j][1] = exp2f(s[rm][j][1] - m_use[0]);
+          s[rm][j][2] = exp2f(s[rm][j][2] - m_use[1]);
+          s[rm][j][3] = exp2f(s[rm][j][3] - m_use[1]);
+          l_run[rm][0] += s[rm][j][0] + s[rm][j][1];
+          l_run[rm][1] += s[rm][j][2] + s[rm][j][3];
         }
       }
+      // O += P V with the weights kept to 16 bits of mantissa: P = P_hi + P_lo, both bfloat16, two products per value
+      // fragment (a weight rounded to bfloat16 alone would carry 8 bits)
 #pragma unroll
       for (int kb2 = 0; kb2 < KT / 16; ++kb2) {
+        uint32_t hi[RM][4], lo[RM][4];
+#pragma unroll
+        for (int rm = 0; rm < RM; ++rm) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            // fragment register q4: rows (q4 & 1 ? +8 : +0), keys 2 tq, 2 tq + 1 of the 8-key block 2 kb2 + (q4 >> 1)
+            const float w0 = s[rm][2 * kb2 + (q4 >> 1)][2 * (q4 & 1)], w1 = s[rm][2 * kb2 + (q4 >> 1)][2 * (q4 & 1) + 1];
+            const __nv_bfloat162 h = __floats2bfloat162_rn(w0, w1);
+            hi[rm][q4] = *reinterpret_cast<const uint32_t*>(&h);
+            lo[rm][q4] = pack_bf16(w0 - __low2float(h), w1 - __high2float(h));
+          }
+        }
         const int tok = kb2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
         for (int n = 0; n < NT; n += 2) {
@@ -199,8 +210,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_mma_kernel(const Dk
             ldmatrix_x4_trans(b0, b1, b2, b3, kbase + tok * ROWS + (((vc0 + n + (lane >> 4)) ^ (tok & 7)) * 16));
 #pragma unroll
             for (int rm = 0; rm < RM; ++rm) {
-              mma_bf16(o[rm][n], pa[rm][kb2], b0, b1);
-              mma_bf16(o[rm][n + 1], pa[rm][kb2], b2, b3);
+              mma_bf16(o[rm][n], hi[rm], b0, b1);
+              mma_bf16(o[rm][n + 1], hi[rm], b2, b3);
+              mma_bf16(o[rm][n], lo[rm], b0, b1);
+              mma_bf16(o[rm][n + 1], lo[rm], b2, b3);
             }
           }
         }
