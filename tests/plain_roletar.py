@@ -15,6 +15,32 @@ import torch
 
 F = torch.float64
 
+# What a 16-bit engine rounds: with ``rounding("bfloat16")`` active, every product's result and every activation between
+# products is rounded to bfloat16 once (and carried on in float64); what the design computes in 32 bit (the residual
+# streams, norms' statistics, scores and softmax weights, step sizes, decays, states) is not.  By default nothing is rounded.
+_round = [lambda x: x]
+
+
+class rounding:
+    def __init__(self, kind):
+        self.fn = (lambda x: x.to(torch.bfloat16).to(F)) if kind == "bfloat16" else (lambda x: x)
+
+    def __enter__(self):
+        self.old = _round[0]
+        _round[0] = self.fn
+
+    def __exit__(self, *a):
+        _round[0] = self.old
+
+
+def rnd(x):
+    return _round[0](x)
+
+
+def lin(h, w):
+    """h W^T, the result rounded as an engine's product would be."""
+    return rnd(h @ w.T)
+
 
 def rms_unit(x, eps):
     """x scaled to unit root mean square over its last axis, eps inside the root."""
@@ -68,9 +94,9 @@ def windowed_sink_attention(h, W, pre, m):
     """Grouped-query attention without positions: sliding window, a per-head sink in the softmax."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ W[pre + "q"].T).view(T, H, dk)
-    k = (h @ W[pre + "k"].T).view(T, G, dk)
-    v = (h @ W[pre + "v"].T).view(T, G, dv)
+    q = lin(h, W[pre + "q"]).view(T, H, dk)
+    k = lin(h, W[pre + "k"]).view(T, G, dk)
+    v = lin(h, W[pre + "v"]).view(T, G, dv)
     window = m["mask"]["size"] if m.get("mask") else None
     vis = causal_mask(T, window)
     out = torch.zeros(T, H, dv, dtype=F)
@@ -79,7 +105,7 @@ def windowed_sink_attention(h, W, pre, m):
         sc = (q[:, hh] @ k[:, g].T) * m["scale"]
         p = softmax_rows(sc, vis, W[pre + "sink"][hh])
         out[:, hh] = p @ v[:, g]
-    return out.reshape(T, H * dv) @ W[pre + "o"].T
+    return lin(rnd(out.reshape(T, H * dv)), W[pre + "o"])
 
 
 def latent_attention(h, W, pre, m, eps):
@@ -88,22 +114,22 @@ def latent_attention(h, W, pre, m, eps):
     T = h.shape[0]
     H, dk, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     pos = torch.arange(T)
-    q = (h @ W[pre + "q"].T).view(T, H, dk + dr)
+    q = lin(h, W[pre + "q"]).view(T, H, dk + dr)
     q_plain, q_rot = q[..., :dk], q[..., dk:]
-    low = h @ W[pre + "dkv"].T
-    c = rms_norm(low[:, :R], W[pre + "dkv.norm"], eps)
+    low = lin(h, W[pre + "dkv"])
+    c = rnd(rms_norm(low[:, :R], W[pre + "dkv.norm"], eps))
     k_rot = low[:, R:]
     base, dims = m["rot"]["base"], m["rot"]["dims"]
-    q_rot = rotate_pairs(q_rot, pos, base, dims)
-    k_rot = rotate_pairs(k_rot, pos, base, dims)
-    k_plain = (c @ W[pre + "uk"].T).view(T, H, dk)
-    v = (c @ W[pre + "uv"].T).view(T, H, dv)
+    q_rot = rnd(rotate_pairs(q_rot, pos, base, dims))
+    k_rot = rnd(rotate_pairs(k_rot, pos, base, dims))
+    k_plain = lin(c, W[pre + "uk"]).view(T, H, dk)
+    v = lin(c, W[pre + "uv"]).view(T, H, dv)
     vis = causal_mask(T)
     out = torch.zeros(T, H, dv, dtype=F)
     for hh in range(H):
         sc = (q_plain[:, hh] @ k_plain[:, hh].T + q_rot[:, hh] @ k_rot.T) * m["scale"]
         out[:, hh] = softmax_rows(sc, vis) @ v[:, hh]
-    return out.reshape(T, H * dv) @ W[pre + "o"].T
+    return lin(rnd(out.reshape(T, H * dv)), W[pre + "o"])
 
 
 def silu(x):
@@ -118,15 +144,15 @@ def selective_scan_mixer(h, W, pre, m):
     """Selective state-space mixer: short causal convolution, input-dependent step size, diagonal decay."""
     T = h.shape[0]
     C_, N, taps, rank = m["inner"], m["state"], m["conv"], m["dt_rank"]
-    xz = h @ W[pre + "in"].T
+    xz = lin(h, W[pre + "in"])
     x, z = xz[:, :C_], xz[:, C_:]
     padded = torch.cat([torch.zeros(taps - 1, C_, dtype=F), x], 0)
     conv = torch.zeros(T, C_, dtype=F)
     for j in range(taps):          # column taps-1 multiplies the current token
         conv += padded[j:j + T] * W[pre + "conv"][:, j][None, :]
-    x = silu(conv + W[pre + "conv.b"][None, :])
-    low = x @ W[pre + "x"].T
-    dt = softplus(low[:, :rank] @ W[pre + "dt"].T + W[pre + "dt.b"][None, :])
+    x = rnd(silu(conv + W[pre + "conv.b"][None, :]))
+    low = lin(x, W[pre + "x"])
+    dt = softplus(lin(low[:, :rank], W[pre + "dt"]) + W[pre + "dt.b"][None, :])
     Bm, Cm = low[:, rank:rank + N], low[:, rank + N:rank + 2 * N]
     A = -torch.exp(W[pre + "A_log"])
     state = torch.zeros(C_, N, dtype=F)
@@ -134,12 +160,12 @@ def selective_scan_mixer(h, W, pre, m):
     for t in range(T):
         state = torch.exp(dt[t][:, None] * A) * state + (dt[t] * x[t])[:, None] * Bm[t][None, :]
         y[t] = state @ Cm[t] + W[pre + "D"] * x[t]
-    return (y * silu(z)) @ W[pre + "o"].T
+    return lin(rnd(y * silu(z)), W[pre + "o"])
 
 
 def dense_ff(h, W, pre):
-    a = torch.relu(h @ W[pre + "up"].T)
-    return (a * a) @ W[pre + "down"].T
+    a = torch.relu(lin(h, W[pre + "up"]))
+    return lin(rnd(a * a), W[pre + "down"])
 
 
 def run_order(cfg):
@@ -179,13 +205,13 @@ def forward(cfg, weights, tokens):
             if S:
                 w_in, w_out, w_mix = W[f"l{li}.{hc}.in"], W[f"l{li}.{hc}.out"], W[f"l{li}.{hc}.mix"]
                 u = sum(w_in[s] * X[s] for s in range(S))
-                y = fn(rms_norm(u, W[f"l{li}.{norm}"], eps))
+                y = fn(rnd(rms_norm(u, W[f"l{li}.{norm}"], eps)))
                 X = [sum(w_mix[s, t] * X[s] for s in range(S)) + w_out[t] * y for t in range(S)]
             else:
-                X = [X[0] + fn(rms_norm(X[0], W[f"l{li}.{norm}"], eps))]
+                X = [X[0] + fn(rnd(rms_norm(X[0], W[f"l{li}.{norm}"], eps)))]
         after.append(sum(X))
     x = sum(X)
-    logits = rms_norm(x, W["final.norm"], eps) @ W["head"].T
+    logits = rnd(rms_norm(x, W["final.norm"], eps)) @ W["head"].T
     cap = cfg.get("logit_softcap")
     if cap:
         logits = cap * torch.tanh(logits / cap)
