@@ -53,10 +53,14 @@ def config(which: str) -> dict:
         return dict(base, vocab=97, width=40, streams=2, layers=[with_mlp(latent(2, 16, 8, 12, 20, base=100.0), None)])
     if which == "only_mlp_streams":   # the stream mixing and the feed-forward dominate: a tiny mixer, four streams
         return dict(base, vocab=97, width=40, streams=4, layers=[with_mlp(attention(1, 1, 8, 8, 3), 56), with_mlp(attention(1, 1, 8, 8, 3), 56)])
+    if which == "odd":      # no size a multiple of 4: every kernel takes its scalar path, five streams, two taps
+        return dict(base, vocab=61, width=50, streams=5, logit_softcap=9.0, loop=dict(start=1, stop=3, times=2), layers=[
+            with_mlp(attention(3, 1, 10, 6, 5, 0.3), 70), with_mlp(mamba(30, 5, 2, 3), None),
+            with_mlp(latent(2, 6, 6, 10, 14, base=300.0, dims=4), 34)])
     raise KeyError(which)
 
 
-PAGE_SIZE = {"mix": 16, "plain": 8, "one": 4, "only_mamba": 16, "only_attention": 8, "only_latent": 8, "only_mlp_streams": 16}
+PAGE_SIZE = {"odd": 2, "mix": 16, "plain": 8, "one": 4, "only_mamba": 16, "only_attention": 8, "only_latent": 8, "only_mlp_streams": 16}
 
 
 def make_weights(cfg: dict, seed: int) -> dict:

@@ -22,7 +22,7 @@ ROOT = Path(__file__).resolve().parent.parent
 # products, which single logits of a small model feel unevenly: there the root mean square of a position's differences is
 # bounded, as a fraction of the root mean square of the request's reference logits.
 TOL = {"float32": 2e-5, "bfloat16": 5e-2}
-LENGTHS = {"mix": [3, 37, 60, 121], "plain": [1, 19, 44, 70], "one": [2, 25, 33, 58], "only_mamba": [1, 9, 40],
+LENGTHS = {"odd": [1, 7, 26, 45], "mix": [3, 37, 60, 121], "plain": [1, 19, 44, 70], "one": [2, 25, 33, 58], "only_mamba": [1, 9, 40],
            "only_attention": [2, 30, 47], "only_latent": [2, 30, 47], "only_mlp_streams": [1, 6, 21]}
 _cache = {}
 
@@ -81,7 +81,7 @@ def compare(results, refs, lengths, dtype, what, noise=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["mix", "plain", "one", "only_mamba", "only_attention", "only_latent", "only_mlp_streams"])
+@pytest.mark.parametrize("which", ["mix", "plain", "one", "odd", "only_mamba", "only_attention", "only_latent", "only_mlp_streams"])
 def test_every_way_of_cutting(tmp_path_factory, which, dtype):
     cfg, W, folder = model(tmp_path_factory, which)
     lengths = LENGTHS[which]

@@ -12,7 +12,7 @@ from delta_b200.config.model_config import ConfigError
 from delta_b200.config.registry import architecture_of
 from delta_b200.models.model import Model
 
-ALL = ["mix", "plain", "one", "only_mamba", "only_attention", "only_latent", "only_mlp_streams"]
+ALL = ["mix", "plain", "one", "odd", "only_mamba", "only_attention", "only_latent", "only_mlp_streams"]
 
 
 def build(which, **engine):
