@@ -165,6 +165,73 @@ __global__ void rows_append_kernel(T* __restrict__ src, int src_stride, const in
   }
 }
 
+// The same step for designs that norm queries and keys: src[t] = [q (H*dk) | k (KV*dk) | v (KV*dv), absent when the
+// value is the key].  One warp per head: the head is read into 32-bit shared memory, rotated on its first rot_dims
+// entries (table == nullptr: not), then divided by its root mean square over dk, sqrt(mean(x^2) + eps) (unit_norm == 0:
+// not), and rounded once.  q goes back in place, k to the cache row.  value_from_key: the value is the key as
+// projected, before rotation and norm (its first dv entries), so no v is read.
+template <typename T>
+__global__ void rows_append_unit_kernel(T* __restrict__ src, int src_stride, const int* __restrict__ tok_pos, const int* __restrict__ tok_row,
+                                        const int* __restrict__ block_table, int max_pages, T* __restrict__ cache, int num_pages,
+                                        const float* __restrict__ table, int table_positions, int rot_dims, int interleaved, int H,
+                                        int KV, int dk, int dv, int ps, int row_width, int k_off, int v_off, int unit_norm, float eps,
+                                        int value_from_key, int* err) {
+  extern __shared__ float heads[];     // [warps][dk]
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int pos = tok_pos[t], b = tok_row[t];
+  T* base = src + (size_t)t * src_stride;
+  if (pos < 0 || (table != nullptr && pos >= table_positions)) {
+    if (threadIdx.x == 0) dk_report(err, DK_DEV_BAD_POSITION, t, pos, table_positions);
+    return;
+  }
+  const long long at = cache != nullptr ? row_slot_of(block_table, max_pages, num_pages, b, pos, ps, t, err) : -1;
+  const long long page = at >= 0 ? at / ps : 0, off = at >= 0 ? at % ps : 0;
+  const int half = rot_dims / 2;
+  float* x = heads + (size_t)warp * dk;
+  for (int hs = warp; hs < H + KV; hs += warps) {
+    T* hp = base + (size_t)hs * dk;
+    const bool is_key = hs >= H;
+    T* crow = (is_key && at >= 0) ? cache + (((size_t)page * KV + (hs - H)) * ps + off) * row_width : nullptr;
+    for (int i = lane; i < dk; i += 32) {
+      const T raw = hp[i];
+      x[i] = to_f32<T>(raw);
+      if (crow != nullptr && value_from_key && i < dv) crow[v_off + i] = raw;
+    }
+    __syncwarp();
+    if (table != nullptr) {
+      const float* cs = table + (size_t)pos * half * 2;
+      for (int j = lane; j < half; j += 32) {
+        int i0, i1;
+        pair_index(j, rot_dims, interleaved, i0, i1);
+        const float u = x[i0], v = x[i1];
+        const float c = cs[2 * j], s = cs[2 * j + 1];
+        x[i0] = u * c - v * s;
+        x[i1] = v * c + u * s;
+      }
+      __syncwarp();
+    }
+    float inv = 1.f;
+    if (unit_norm) {
+      float ss = 0.f;
+      for (int i = lane; i < dk; i += 32) ss += x[i] * x[i];
+      ss = warp_sum(ss);
+      inv = 1.f / sqrtf(ss / (float)dk + eps);
+    }
+    for (int i = lane; i < dk; i += 32) {
+      const T r = from_f32<T>(x[i] * inv);
+      if (!is_key) hp[i] = r;
+      else if (crow != nullptr) crow[k_off + i] = r;
+    }
+    __syncwarp();
+  }
+  if (at < 0 || value_from_key) return;
+  const T* vsrc = base + (size_t)(H + KV) * dk;
+  for (int idx = threadIdx.x; idx < KV * dv; idx += blockDim.x) {
+    const int g = idx / dv, i = idx - g * dv;
+    cache[(((size_t)page * KV + g) * ps + off) * row_width + v_off + i] = vsrc[idx];
+  }
+}
+
 // Latent attention's step between its first product and the attention kernel.
 // src[t] = [per head: q_plain (dq) | q_rot (dr)] x H, then [low (R) | k_rot (dr)].
 //   c      = low * rsqrt(mean(low^2) + eps) * w      (32 bit)   -> cache row [0, R)
@@ -267,6 +334,31 @@ extern "C" int dk_rows_append(void* src, int src_stride, const int* tok_pos, con
   else DK_REQUIRE(false, "rows_append: unknown dtype %d", dtype);
 #undef LAUNCH
   return dk_check_launch("rows_append");
+}
+
+extern "C" int dk_rows_append_unit(void* src, int src_stride, const int* tok_pos, const int* tok_row, const int* block_table,
+                                   int max_pages, void* cache, int num_pages, const float* table, int table_positions, int rot_dims,
+                                   int interleaved, int T_, int H, int KV, int dk, int dv, int ps, int row_width, int k_off, int v_off,
+                                   int unit_norm, float eps, int value_from_key, int dtype, int* err, cudaStream_t stream) {
+  if (T_ == 0) return 0;
+  DK_REQUIRE(T_ > 0 && H > 0 && KV > 0 && dk > 0 && dv > 0 && ps > 0, "rows_append_unit: bad sizes T=%d H=%d KV=%d dk=%d dv=%d ps=%d", T_, H, KV, dk, dv, ps);
+  DK_REQUIRE(src_stride >= (H + KV) * dk + (value_from_key ? 0 : KV * dv), "rows_append_unit: rows of %d elements do not hold q, k and v", src_stride);
+  DK_REQUIRE(!value_from_key || dv <= dk, "rows_append_unit: a value of %d entries cannot be taken from a key of %d", dv, dk);
+  DK_REQUIRE(cache == nullptr || (block_table != nullptr && max_pages > 0 && num_pages > 0), "rows_append_unit: a cache is given without a block table");
+  DK_REQUIRE(table == nullptr || (rot_dims > 0 && rot_dims % 2 == 0 && rot_dims <= dk), "rows_append_unit: %d rotated entries do not fit a head of %d", rot_dims, dk);
+  DK_REQUIRE(k_off + dk <= row_width && v_off + dv <= row_width, "rows_append_unit: key and value do not fit a row of %d", row_width);
+  const int threads = (H + KV) >= 8 ? 256 : 128;
+  const size_t smem = (size_t)(threads / 32) * dk * sizeof(float);
+  DK_REQUIRE(smem <= 48 * 1024, "rows_append_unit: heads of %d entries do not fit the shared memory", dk);
+#define LAUNCH(T)                                                                                                                 \
+  rows_append_unit_kernel<T><<<T_, threads, smem, stream>>>((T*)src, src_stride, tok_pos, tok_row, block_table, max_pages, (T*)cache, \
+                                                            num_pages, table, table_positions, rot_dims, interleaved, H, KV, dk, dv, \
+                                                            ps, row_width, k_off, v_off, unit_norm, eps, value_from_key, err)
+  if (dtype == DK_F32) LAUNCH(float);
+  else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
+  else DK_REQUIRE(false, "rows_append_unit: unknown dtype %d", dtype);
+#undef LAUNCH
+  return dk_check_launch("rows_append_unit");
 }
 
 extern "C" int dk_latent_prepare(const void* src, int src_stride, const int* tok_pos, const int* tok_row, const int* block_table,

@@ -88,6 +88,19 @@ _SIGNATURES = {
     "dk_gemm_stream_k_supported": [I, I, I, I],
     "dk_gemm_stream_k": [P, P, P, I, I, I, I, I, I, I, I, P, P, P],
     "dk_wait_check": [P, C.c_longlong, P],
+    "dk_embedding_pair": [P, P, P, P, P, P, P, F, P, L, L, L, P, P, I, I, I, I, P, P],
+    "dk_remember_tokens": [P, P, P, P, P, I, P],
+    "dk_residual_norm": [P, P, P, P, P, P, P, P, I, I, F, I, I, I, I, P],
+    "dk_rows_append_unit": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, F, I, I, P, P],
+    "dk_decay_attention_slice": [I, I, I, I],
+    "dk_decay_attention": [P, I, I, I, I, I, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "dk_gated_rms_norm": [P, P, I, P, P, I, I, F, I, P],
+    "dk_glu_clamped": [P, P, L, I, F, F, F, I, P],
+    "dk_router_topk": [P, I, P, P, I, I, I, P],
+    "dk_experts_align": [P, I, I, P, I, P, I, P],
+    "dk_experts_gemm": [P, P, P, P, P, I, I, I, I, I, F, F, F, I, P],
+    "dk_experts_combine": [P, P, I, P, P, I, P, I, I, I, P],
+    "dk_experts_tile_rows": [],
 }
 
 

@@ -596,3 +596,153 @@ def attention_rows_mma(params: RowAttnParams, max_m: int, splits: int = 1, scrat
     through.  ``splits`` > 1: that many blocks share a row's keys and ``scratch`` (float32) takes their partial results."""
     _l.check(_l.load().dk_attention_rows_mma(C.byref(params), int(max_m), int(splits), _ptr(scratch, "scratch", torch.float32),
                                              _stream()), "attention_rows_mma", 2 if splits > 1 else 1)
+
+
+def rows_append_unit(src, tok_pos, tok_row, block_table, cache, *, H, KV, dk, dv, ps, row_width, k_off, v_off, table=None,
+                     rot_dims=0, interleaved=True, unit_eps=None, value_from_key=False, err=None):
+    """As ``rows_append``, one warp per head in 32 bit: after the rotation every query and key head is divided by its root
+    mean square, sqrt(mean(x^2) + ``unit_eps``) (None: not), and rounded once.  ``value_from_key``: ``src`` holds no v;
+    the value is the key as it was projected, before rotation and norm."""
+    T = src.shape[0]
+    if cache is not None and (tuple(cache.shape[1:]) != (KV, ps, row_width) or cache.dtype != src.dtype):
+        raise KernelError(f"rows_append_unit: cache has shape {tuple(cache.shape)} / {cache.dtype}, expected [pages, {KV}, {ps}, {row_width}] of {src.dtype}")
+    if table is not None and tuple(table.shape[1:]) != (rot_dims // 2, 2):
+        raise KernelError(f"rows_append_unit: table has shape {tuple(table.shape)}, expected [positions, {rot_dims // 2}, 2]")
+    i32 = torch.int32
+    _l.check(_l.load().dk_rows_append_unit(
+        _ptr(src, "src"), src.shape[1], _ptr(tok_pos, "tok_pos", i32), _ptr(tok_row, "tok_row", i32),
+        _ptr(block_table, "block_table", i32), block_table.shape[1] if block_table is not None else 0, _ptr(cache, "cache"),
+        cache.shape[0] if cache is not None else 0, _ptr(table, "table", torch.float32), table.shape[0] if table is not None else 0,
+        int(rot_dims), int(bool(interleaved)), T, H, KV, dk, dv, ps, row_width, k_off, v_off, int(unit_eps is not None),
+        float(unit_eps or 0.0), int(bool(value_from_key)), dtype_code(src.dtype), _ptr(err, "err", i32), _stream()), "rows_append_unit")
+
+
+# ---- a residual stream of one 32-bit copy whose sublayers run side by side ---------------------------------------
+
+NORM_KINDS = {"rms": 0, "layer": 1}
+
+
+def embedding_pair(tokens, table, X, *, scale=1.0, pair_table=None, buckets=0, mul_prev=0, mul_cur=0, prev_state=None, tok_row=None,
+                   tok_pos=None, row_q_start=None, row_slot=None, keep=None, err=None):
+    """X[t] = table[tokens[t]] * scale (+ pair_table[(previous token * mul_prev + token * mul_cur) mod buckets]; a request's
+    first token takes row ``buckets``; the token before a portion's first comes from ``prev_state`` [slots, 1]).  X, and
+    ``keep`` when given (a second copy), are float32 [T, d]."""
+    T, d = X.shape
+    i32 = torch.int32
+    _l.check(_l.load().dk_embedding_pair(
+        _ptr(tokens, "tokens", i32), _ptr(tok_row, "tok_row", i32), _ptr(tok_pos, "tok_pos", i32), _ptr(row_q_start, "row_q_start", i32),
+        _ptr(row_slot, "row_slot", i32), _ptr(prev_state, "prev_state", i32), _ptr(table, "table"), float(scale),
+        _ptr(pair_table, "pair_table", table.dtype), int(buckets), int(mul_prev), int(mul_cur), _ptr(X, "X", torch.float32),
+        _ptr(keep, "keep", torch.float32), T, d, table.shape[0], dtype_code(table.dtype), _ptr(err, "err", i32), _stream()), "embedding_pair")
+    return X
+
+
+def remember_tokens(tokens, prev_state, *, row_q_start, row_q_len, row_slot):
+    """prev_state[slot of row] = the row's last token of this step."""
+    i32 = torch.int32
+    _l.check(_l.load().dk_remember_tokens(_ptr(tokens, "tokens", i32), _ptr(row_q_start, "row_q_start", i32), _ptr(row_q_len, "row_q_len", i32),
+                                          _ptr(row_slot, "row_slot", i32), _ptr(prev_state, "prev_state", i32), row_slot.shape[0], _stream()),
+             "remember_tokens")
+
+
+def residual_norm(X, out, *, updates=(), extra=None, vec=None, weight=None, eps=0.0, kind="layer", rows=None, write_back=True):
+    """The step between two layers on a 32-bit stream X [T, d]:  X <- X + (y1 + y2) (``updates``: none, one or two tensors
+    of the compute type), X <- X + ``extra`` (float32 [T, d]), X <- X + ``vec`` (float32 [d]), stored when ``write_back``;
+    then ``out`` = norm(X) * weight with the layer norm without bias or the RMS norm (``weight`` None: X itself).
+    ``rows``: only these tokens, in this order.  ``out`` None: only the sums are done."""
+    T, d = X.shape
+    n = rows.shape[0] if rows is not None else T
+    if len(updates) > 2:
+        raise KernelError("residual_norm takes at most two updates")
+    for y in updates:
+        if tuple(y.shape) != (T, d):
+            raise KernelError(f"residual_norm: an update has shape {tuple(y.shape)}, the stream {(T, d)}")
+    if out is not None and tuple(out.shape) != (n, d):
+        raise KernelError(f"residual_norm: the output has shape {tuple(out.shape)}, expected {(n, d)}")
+    y1 = updates[0] if len(updates) > 0 else None
+    y2 = updates[1] if len(updates) > 1 else None
+    f32 = torch.float32
+    ydt = dtype_code(y1.dtype) if y1 is not None else (dtype_code(out.dtype) if out is not None and out.dtype != f32 else F32)
+    _l.check(_l.load().dk_residual_norm(
+        _ptr(X, "X", f32), _ptr(y1, "update"), _ptr(y2, "update", y1.dtype if y1 is not None else None), _ptr(extra, "extra", f32),
+        _ptr(vec, "vec", f32), _ptr(weight, "weight", f32), _ptr(out, "out"), _ptr(rows, "rows", torch.int32), n, d, float(eps),
+        NORM_KINDS[kind], int(bool(write_back)), ydt, dtype_code(out.dtype) if out is not None else F32, _stream()), "residual_norm")
+    return out
+
+
+# ---- linear attention with a decay per head ---------------------------------------------------------------------
+
+def decay_attention_slice(rows, H, dk, dv) -> int:
+    return int(_l.load().dk_decay_attention_slice(int(rows), H, dk, dv))
+
+
+def decay_attention(src, q_off, k_off, v_off, decays, state, out, *, H, dk, dv, row_slot, row_q_start, row_q_len, silu=True, slice_=None):
+    """Per row and head the recurrence  S <- decay_h S + k v^T,  o = S^T q  over the row's new tokens, from and into
+    ``state`` [slots, H, dk, dv] (float32).  ``src`` [T, stride] holds a token's q at ``q_off``, k at ``k_off`` (H*dk each) and
+    v at ``v_off`` (H*dv), before the activation when ``silu``; ``decays`` [H] float64; ``out`` float32 [T, H*dv]."""
+    rows = row_slot.shape[0]
+    if tuple(state.shape[1:]) != (H, dk, dv):
+        raise KernelError(f"decay_attention: the state has shape {tuple(state.shape)}, expected [slots, {H}, {dk}, {dv}]")
+    if tuple(out.shape) != (src.shape[0], H * dv):
+        raise KernelError(f"decay_attention: the output has shape {tuple(out.shape)}, expected {(src.shape[0], H * dv)}")
+    dvs = slice_ or decay_attention_slice(rows, H, dk, dv)
+    i32 = torch.int32
+    _l.check(_l.load().dk_decay_attention(
+        _ptr(src, "src"), src.shape[1], int(q_off), int(k_off), int(v_off), int(bool(silu)), _ptr(decays, "decays", torch.float64),
+        _ptr(state, "state", torch.float32), _ptr(out, "out", torch.float32), _ptr(row_slot, "row_slot", i32),
+        _ptr(row_q_start, "row_q_start", i32), _ptr(row_q_len, "row_q_len", i32), rows, H, dk, dv, dvs, dtype_code(src.dtype),
+        _stream()), "decay_attention")
+    return out
+
+
+def gated_rms_norm(o, gate_ptr, gate_stride, weight, out, eps):
+    """out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate) per token; ``o`` float32 [T, n]; the gate's n values of a token
+    lie at ``gate_ptr`` + t * ``gate_stride`` elements of the type of ``out``."""
+    T, n = o.shape
+    _l.check(_l.load().dk_gated_rms_norm(_ptr(o, "o", torch.float32), gate_ptr, int(gate_stride), _ptr(weight, "weight", torch.float32),
+                                         _ptr(out, "out"), T, n, float(eps), dtype_code(out.dtype), _stream()), "gated_rms_norm")
+    return out
+
+
+# ---- gated feed-forwards and a mixture of experts ---------------------------------------------------------------
+
+def glu_clamped(gate_up, out, limit=0.0, alpha=1.702, shift=1.0):
+    """out = g' * sigmoid(alpha g') * (u' + shift) from rows [g | u], g' = min(g, limit), u' = clamp(u, -limit, limit)
+    (``limit`` 0: unclamped)."""
+    rows, F2 = gate_up.shape
+    _l.check(_l.load().dk_glu_clamped(_ptr(gate_up, "gate_up"), _ptr(out, "out", gate_up.dtype), rows, F2 // 2, float(limit), float(alpha),
+                                      float(shift), dtype_code(gate_up.dtype), _stream()), "glu_clamped")
+    return out
+
+
+def router_topk(logits, experts, top, choice, weight):
+    """Per token the ``top`` largest of the first ``experts`` columns of float32 ``logits`` and the softmax over them."""
+    T = logits.shape[0]
+    _l.check(_l.load().dk_router_topk(_ptr(logits, "logits", torch.float32), logits.shape[1], _ptr(choice, "choice", torch.int32),
+                                      _ptr(weight, "weight", torch.float32), T, int(experts), int(top), _stream()), "router_topk")
+
+
+def experts_tile_rows() -> int:
+    return int(_l.load().dk_experts_tile_rows())
+
+
+def experts_align(choice, experts, sorted_slots, tile_expert):
+    _l.check(_l.load().dk_experts_align(_ptr(choice, "choice", torch.int32), choice.numel(), int(experts),
+                                        _ptr(sorted_slots, "sorted_slots", torch.int32), sorted_slots.numel(),
+                                        _ptr(tile_expert, "tile_expert", torch.int32), tile_expert.numel(), _stream()), "experts_align")
+
+
+def experts_gemm(a, w, out, sorted_slots, tile_expert, *, top, n, k, act=False, limit=0.0, alpha=1.702, shift=1.0):
+    """For every tile of rows its expert's product (see ``csrc/experts.cu``); ``w`` is [E, n (2n with ``act``), k]."""
+    _l.check(_l.load().dk_experts_gemm(_ptr(a, "a"), _ptr(w, "w", a.dtype), _ptr(out, "out"), _ptr(sorted_slots, "sorted_slots", torch.int32),
+                                       _ptr(tile_expert, "tile_expert", torch.int32), tile_expert.numel(), int(top), int(n), int(k),
+                                       int(bool(act)), float(limit), float(alpha), float(shift), dtype_code(a.dtype), _stream()), "experts_gemm")
+
+
+def experts_combine(z, weight, out, shared=None, gate_logit=None, gate_stride=0):
+    """out[t] = sum_j weight[t, j] z[t*top + j] (+ sigmoid(gate logit of t) * shared[t]); ``gate_logit``: an address (float32)."""
+    T, d = out.shape
+    _l.check(_l.load().dk_experts_combine(_ptr(z, "z", torch.float32), _ptr(weight, "weight", torch.float32), weight.shape[1],
+                                          _ptr(shared, "shared", out.dtype), gate_logit, int(gate_stride), _ptr(out, "out"), T, d,
+                                          dtype_code(out.dtype), _stream()), "experts_combine")
+    return out

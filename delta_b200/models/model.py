@@ -32,7 +32,7 @@ class Model:
         # run order with every entry's cache index resolved
         self.order: List[RunEntry] = []
         for n, e in enumerate(spec.order):
-            self.order.append(RunEntry(e.layer, e.cache if e.cache is not None else n, e.writes_cache))
+            self.order.append(RunEntry(e.layer, e.cache if e.cache is not None else n, e.writes_cache, e.enters_pass))
         writers = {e.cache for e in self.order if e.writes_cache}
         for e in self.order:
             if not e.writes_cache and e.cache not in writers:
@@ -108,6 +108,8 @@ class Model:
         totals = ctx.capture.get("layer_totals") if ctx.capture is not None else None
         for e in self.order:
             block = self.blocks[e.layer]
+            if e.enters_pass is not None:
+                x, pending = self.stream.enter_pass(ctx, x, pending, e.enters_pass)
             cache = ctx.cache_view(e.cache, e.writes_cache) if block.cache_spec() is not None else None
             names = block.run_state_specs()
             if names:

@@ -20,10 +20,12 @@ class LayerSpec:
 class RunEntry:
     """One run of a layer.  ``cache`` names the cache the run uses (an index of its
     own by default); ``writes_cache`` False makes the run read a cache that another
-    run filled instead of appending its own keys and values."""
+    run filled instead of appending its own keys and values.  ``enters_pass`` n: before this run the residual stream's
+    ``enter_pass(ctx, x, pending, n)`` is called (what a design adds to the stream whenever a repeated span starts over)."""
     layer: int
     cache: Optional[int] = None
     writes_cache: bool = True
+    enters_pass: Optional[int] = None   # this run is the first of pass number ... of a repeated span: the stream is told first
 
 
 @dataclass(frozen=True)

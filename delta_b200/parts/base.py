@@ -209,6 +209,11 @@ class Stream(Part):
     def start(self, ctx, table):
         raise NotImplementedError
 
+    def enter_pass(self, ctx, x, pending, number: int):
+        """Called before the first layer of pass ``number`` of a span of layers that runs several times; returns
+        (x, pending).  Streams of models without such a span never see it."""
+        raise NotImplementedError(f"{type(self).__name__} has nothing to do at the start of a pass")
+
     def finish(self, ctx, x, pending, norm, rows):
         raise NotImplementedError
 

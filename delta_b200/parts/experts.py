@@ -1,0 +1,84 @@
+"""A mixture of experts: every token runs ``top`` of ``experts`` small gated feed-forwards, chosen by a router.
+
+    z = W_router h                                   router logits, 32 bit
+    the ``top`` largest z pick the experts; their weights are the softmax over the chosen logits only
+    expert e:  y = act(W_gate,e h, W_up,e h),  W_down,e y          (the gated activation of ``clamped_glu``)
+    out = sum over the chosen experts of weight * expert(h)  (+ sigmoid(w_sg . h) * shared(h) when there is a shared expert,
+          a feed-forward of the same form that every token runs)
+Nothing about the routing is read on the host: the (token, choice) pairs are sorted by expert on the device into tiles of
+rows of one expert, and the two products of all experts are one launch each (``csrc/experts.cu``).  The router's rows and
+the shared expert's gate row are one matrix, so one product gives both.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from . import linear
+from .base import FEED_FORWARDS, FeedForward, TensorSpec
+from .feed_forward import ClampedGLU
+
+
+@FEED_FORWARDS.register("experts")
+class Experts(FeedForward):
+    """Tensor names under ``prefix``: ``router`` [E, d]; ``e<i>.gate|up`` [F, d], ``e<i>.down`` [d, F]; with a shared expert
+    ``shared.gate|up|down`` and ``shared.sg`` [1, d]."""
+
+    def __init__(self, prefix: str, width: int, experts: int, top: int, intermediate: int, limit: float = 0.0, alpha: float = 1.702,
+                 shift: float = 1.0, shared: Optional[dict] = None):
+        self.prefix, self.width = prefix, int(width)
+        self.experts, self.top, self.intermediate = int(experts), int(top), int(intermediate)
+        if not (1 <= self.top <= self.experts):
+            raise ValueError(f"{self.top} of {self.experts} experts cannot be chosen")
+        self.limit, self.alpha, self.shift = float(limit or 0.0), float(alpha), float(shift)
+        self.shared = None
+        if shared:
+            self.shared = ClampedGLU(prefix + "shared.", width, int(shared["intermediate"]), limit=shared.get("limit", 0.0),
+                                     alpha=shared.get("alpha", alpha), shift=shared.get("shift", shift))
+        self.w_router = self.w1 = self.w2 = None
+
+    def tensor_specs(self):
+        p, d, F = self.prefix, self.width, self.intermediate
+        specs = [TensorSpec(p + "router", (self.experts, d))]
+        for e in range(self.experts):
+            specs += [TensorSpec(f"{p}e{e}.gate", (F, d)), TensorSpec(f"{p}e{e}.up", (F, d)), TensorSpec(f"{p}e{e}.down", (d, F))]
+        if self.shared is not None:
+            specs += self.shared.tensor_specs() + [TensorSpec(p + "shared.sg", (1, d))]
+        return specs
+
+    def bind(self, tensors):
+        p = self.prefix
+        rows = [tensors[p + "router"]] + ([tensors[p + "shared.sg"]] if self.shared is not None else [])
+        self.w_router = torch.cat(rows, dim=0).contiguous()
+        self.w1 = torch.stack([torch.cat([tensors[f"{p}e{e}.gate"], tensors[f"{p}e{e}.up"]], dim=0) for e in range(self.experts)]).contiguous()
+        self.w2 = torch.stack([tensors[f"{p}e{e}.down"] for e in range(self.experts)]).contiguous()
+        if self.shared is not None:
+            self.shared.bind(tensors)
+
+    def forward(self, ctx, x):
+        T, d, E, top, F = x.shape[0], self.width, self.experts, self.top, self.intermediate
+        dev, i32, f32 = x.device, torch.int32, torch.float32
+        z = linear.linear(ctx, x, self.w_router, out_dtype=f32)          # [T, E (+1)]
+        choice = torch.empty((T, top), dtype=i32, device=dev)
+        weight = torch.empty((T, top), dtype=f32, device=dev)
+        ops.router_topk(z, E, top, choice, weight)
+        tile = ops.experts_tile_rows()
+        slots = T * top
+        capacity = -(-(slots + (tile - 1) * min(E, slots)) // tile) * tile
+        sorted_slots = torch.empty(capacity, dtype=i32, device=dev)
+        tile_expert = torch.empty(capacity // tile, dtype=i32, device=dev)
+        ops.experts_align(choice, E, sorted_slots, tile_expert)
+        y = torch.empty((capacity, F), dtype=x.dtype, device=dev)
+        ops.experts_gemm(x, self.w1, y, sorted_slots, tile_expert, top=top, n=F, k=d, act=True, limit=self.limit, alpha=self.alpha,
+                         shift=self.shift)
+        out_slots = torch.empty((slots, d), dtype=f32, device=dev)
+        ops.experts_gemm(y, self.w2, out_slots, sorted_slots, tile_expert, top=top, n=d, k=F)
+        out = torch.empty((T, d), dtype=x.dtype, device=dev)
+        if self.shared is not None:
+            s = self.shared.forward(ctx, x)
+            ops.experts_combine(out_slots, weight, out, shared=s, gate_logit=z.data_ptr() + E * 4, gate_stride=z.shape[1])
+        else:
+            ops.experts_combine(out_slots, weight, out)
+        return out

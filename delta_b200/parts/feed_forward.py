@@ -1,5 +1,6 @@
 """SwiGLU feed-forward:  down( silu(gate x) * (up x) )
-(reference: DELTA/Engine/DELTA/model.py:495-518, ``w2(silu(w1 x) * w3 x)``)."""
+(reference: DELTA/Engine/DELTA/model.py:495-518, ``w2(silu(w1 x) * w3 x)``), a dense feed-forward with one of several
+activations, and a gated one with clamped branches."""
 from __future__ import annotations
 
 import torch
@@ -65,3 +66,29 @@ class DenseMLP(FeedForward):
         h = linear.linear(ctx, x, self.w_up)
         ops.activation(h, h, self.activation)
         return linear.linear(ctx, h, self.w_down)
+
+
+@FEED_FORWARDS.register("clamped_glu")
+class ClampedGLU(FeedForward):
+    """down( g' * sigmoid(alpha g') * (u' + shift) ) with g' = min(gate x, limit) and u' = clamp(up x, -limit, limit)
+    (``limit`` 0: unclamped).  Tensor names: ``<prefix>gate``, ``<prefix>up`` [I, d] and ``<prefix>down`` [d, I]."""
+
+    def __init__(self, prefix: str, width: int, intermediate: int, limit: float = 0.0, alpha: float = 1.702, shift: float = 1.0):
+        self.prefix, self.width, self.intermediate = prefix, int(width), int(intermediate)
+        self.limit, self.alpha, self.shift = float(limit or 0.0), float(alpha), float(shift)
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self):
+        p, d, i = self.prefix, self.width, self.intermediate
+        return [TensorSpec(p + "gate", (i, d)), TensorSpec(p + "up", (i, d)), TensorSpec(p + "down", (d, i))]
+
+    def bind(self, tensors):
+        p = self.prefix
+        self.w_gate_up = torch.cat([tensors[p + "gate"], tensors[p + "up"]], dim=0).contiguous()
+        self.w_down = tensors[p + "down"]
+
+    def forward(self, ctx, x):
+        gu = linear.linear(ctx, x, self.w_gate_up)
+        act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+        ops.glu_clamped(gu, act, self.limit, self.alpha, self.shift)
+        return linear.linear(ctx, act, self.w_down)

@@ -1,5 +1,6 @@
 """RMSNorm: x * rsqrt(mean(x^2) + eps) * weight, the statistics in 32 bit
-(reference: DELTA/Engine/DELTA/model.py:521-532)."""
+(reference: DELTA/Engine/DELTA/model.py:521-532), and the layer norm without bias,
+(x - mean) / sqrt(var + eps) * weight with var the mean of the squared deviations."""
 from __future__ import annotations
 
 import torch
@@ -13,6 +14,8 @@ class RMSNorm(Norm):
     """``width`` and ``eps`` are parameters.  ``cast_before_weight`` keeps the order of
     the reference in reduced precision: the normalised value is rounded to the
     activation type before it is multiplied by the weight (model.py:531-532)."""
+
+    kind = "rms"       # what a kernel that normalises a 32-bit stream is told
 
     def __init__(self, name: str, width: int, eps: float, cast_before_weight: bool = True):
         self.name = name
@@ -40,3 +43,36 @@ class RMSNorm(Norm):
         out = torch.empty((n, self.width), dtype=x.dtype, device=x.device)
         cast_first = self.cast_before_weight and x.dtype != torch.float32
         return ops.rms_norm(x, self.weight, self.eps, out, add=add, rows=rows, cast_first=cast_first)
+
+
+@NORMS.register("layer_norm")
+class LayerNorm(Norm):
+    """Layer norm with a weight and no bias.  It reads a 32-bit residual stream (``parts/residual.py``), whose kernel
+    takes the mean and the squared deviations in two passes over the row; it has no kernel for a stream in the compute
+    type, so a model with the ``single`` stream cannot name it."""
+    kind = "layer"
+
+    def __init__(self, name: str, width: int, eps: float):
+        self.name, self.width, self.eps = name, int(width), float(eps)
+        self.weight = None
+        self._weight32 = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.width,), kind="vector", init="norm")]
+
+    def bind(self, tensors):
+        self.weight = tensors[self.name]
+        self._weight32 = None
+
+    def weight32(self):
+        if self._weight32 is None:
+            self._weight32 = self.weight.float().contiguous()
+        return self._weight32
+
+    def forward(self, ctx, x, add=None, rows=None):
+        if x.dtype != torch.float32:
+            raise TypeError("layer_norm reads a 32-bit residual stream (stream 'residual_f32')")
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.width), dtype=ctx.dtype, device=x.device)
+        return ops.residual_norm(x, out, updates=() if add is None else (add,), weight=self.weight32(), eps=self.eps, kind="layer",
+                                 rows=rows, write_back=rows is None)

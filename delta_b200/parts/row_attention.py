@@ -8,7 +8,12 @@ key-value head h // (H / kv_heads)), with the options
         p_j = exp(s_j) / (exp(sink_h) + sum_j' exp(s_j'));
   * ``position``: a rotary position encoding on the first ``rot_dims`` entries of every query and key head
     (None: positions do not enter the scores);
-  * ``scale``: the factor on q . k (default 1 / sqrt(head_dim)).
+  * ``scale``: the factor on q . k (default 1 / sqrt(head_dim));
+  * ``sink_logit``: a sink with this fixed logit for every head and no tensor (0: the softmax has one more in its
+    denominator), instead of ``sink``;
+  * ``unit_norm_eps``: after the rotation every query and key head is divided by its root mean square,
+    sqrt(mean(x^2) + eps), with no weight (None: not);
+  * ``value_from_key``: there is no value projection; a token's value is its key as projected, before rotation and norm.
 Scores and softmax weights are 32 bit in every kernel of the family.  ``run`` chooses the kernels for a batch.
 """
 from __future__ import annotations
@@ -87,7 +92,8 @@ class SinkAttention(Mixer):
 
     def __init__(self, prefix: str, width: int, heads: int, kv_heads: int, head_dim: int, value_dim: Optional[int] = None,
                  window: Optional[int] = None, sink: bool = False, scale: Optional[float] = None,
-                 position: Optional[PartSpec] = None, rot_dims: Optional[int] = None, names: Optional[dict] = None):
+                 position: Optional[PartSpec] = None, rot_dims: Optional[int] = None, names: Optional[dict] = None,
+                 sink_logit: Optional[float] = None, unit_norm_eps: Optional[float] = None, value_from_key: bool = False):
         if heads % kv_heads:
             raise ValueError(f"{heads} heads are no multiple of {kv_heads} key-value heads")
         self.prefix, self.width = prefix, int(width)
@@ -95,6 +101,13 @@ class SinkAttention(Mixer):
         self.dv = int(value_dim) if value_dim else self.dk
         self.window = int(window) if window else None
         self.has_sink = bool(sink)
+        self.sink_logit = float(sink_logit) if sink_logit is not None else None
+        self.unit_norm_eps = float(unit_norm_eps) if unit_norm_eps is not None else None
+        self.value_from_key = bool(value_from_key)
+        if self.has_sink and self.sink_logit is not None:
+            raise ValueError("a learned sink and a fixed sink logit exclude one another")
+        if self.value_from_key and self.dv != self.dk:
+            raise ValueError(f"values taken from keys have the keys' size: {self.dv} against {self.dk}")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.dk)
         self.position = position.build(POSITION_ENCODINGS) if position is not None else None
         self.rot_dims = int(rot_dims) if rot_dims else (self.dk if position is not None else 0)
@@ -104,17 +117,22 @@ class SinkAttention(Mixer):
 
     def tensor_specs(self):
         p, n, d = self.prefix, self.names, self.width
-        specs = [TensorSpec(p + n["q"], (self.heads * self.dk, d)), TensorSpec(p + n["k"], (self.kv_heads * self.dk, d)),
-                 TensorSpec(p + n["v"], (self.kv_heads * self.dv, d)), TensorSpec(p + n["o"], (d, self.heads * self.dv))]
+        specs = [TensorSpec(p + n["q"], (self.heads * self.dk, d)), TensorSpec(p + n["k"], (self.kv_heads * self.dk, d))]
+        if not self.value_from_key:
+            specs.append(TensorSpec(p + n["v"], (self.kv_heads * self.dv, d)))
+        specs.append(TensorSpec(p + n["o"], (d, self.heads * self.dv)))
         if self.has_sink:
             specs.append(TensorSpec(p + n["sink"], (self.heads,), kind="vector", init="uniform:-1:1"))
         return specs
 
     def bind(self, tensors):
         p, n = self.prefix, self.names
-        self.w_qkv = torch.cat([tensors[p + n["q"]], tensors[p + n["k"]], tensors[p + n["v"]]], dim=0).contiguous()
+        mats = [tensors[p + n["q"]], tensors[p + n["k"]]] + ([] if self.value_from_key else [tensors[p + n["v"]]])
+        self.w_qkv = torch.cat(mats, dim=0).contiguous()
         self.w_o = tensors[p + n["o"]]
         self.sink = tensors[p + n["sink"]].float().contiguous() if self.has_sink else None
+        if self.sink_logit is not None:
+            self.sink = torch.full((self.heads,), self.sink_logit, dtype=torch.float32, device=self.w_o.device)
 
     def cache_spec(self):
         # a page of a layer: [kv head][offset in the page][key | value]
@@ -124,9 +142,14 @@ class SinkAttention(Mixer):
         H, KV, dk, dv = self.heads, self.kv_heads, self.dk, self.dv
         qkv = linear.linear(ctx, x, self.w_qkv)
         table = self.position.table(x.device) if self.position is not None else None
-        ops.rows_append(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, cache.pages if cache.writes else None, H=H, KV=KV,
-                        dk=dk, dv=dv, ps=cache.page_size, row_width=dk + dv, k_off=0, v_off=dk, table=table,
-                        rot_dims=self.rot_dims, interleaved=bool(getattr(self.position, "interleaved", True)), err=ctx.err)
+        append = dict(H=H, KV=KV, dk=dk, dv=dv, ps=cache.page_size, row_width=dk + dv, k_off=0, v_off=dk, table=table,
+                      rot_dims=self.rot_dims, interleaved=bool(getattr(self.position, "interleaved", True)), err=ctx.err)
+        pages = cache.pages if cache.writes else None
+        if self.unit_norm_eps is not None or self.value_from_key:
+            ops.rows_append_unit(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, pages, unit_eps=self.unit_norm_eps,
+                                 value_from_key=self.value_from_key, **append)
+        else:
+            ops.rows_append(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, pages, **append)
         out = torch.empty((x.shape[0], H * dv), dtype=x.dtype, device=x.device)
         params = make_params(ctx, q=qkv, q_stride=qkv.shape[1], q_head_stride=dk, out=out, cache=cache, H=H, KV=KV, dk=dk, dv=dv,
                              row_width=dk + dv, k_off=0, v_off=dk, scale=self.scale, window=self.window, sink=self.sink)
