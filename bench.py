@@ -52,6 +52,10 @@ Other workloads (``--workload``), each printing one JSON line of the same shape:
                decode at batch 8, context 2,048, through ``ModelRunner.step``; then every launcher's share of
                one such step with the fraction of the peaks that the elementwise and attention kernels reach
 
+  pibalorn     the Pibalorn design (32-bit residual stream, parallel blocks, attention whose values are its keys,
+               linear attention with a decay per head, mixtures of experts; random weights at widths ``--width``)
+               beside the Yi architecture, measured as the roletar workload is
+
 ``--impl reference`` runs the unmodified hoenza/DELTA engine (baseline/reference_arm.py) on the
 default workload and prints its line.
 """
@@ -400,8 +404,27 @@ def yi_like_config(d: int, layers: int) -> dict:
                 intermediate_size=(8 * d // 3 + 255) // 256 * 256, vocab_size=32000, max_position_embeddings=8192)
 
 
+def pibalorn_config(d: int) -> dict:
+    """A Pibalorn model with layers of the sizes of a real model of width d: a linear-attention layer with a dense gated
+    feed-forward, then an attention layer and a linear-attention layer with mixtures of 16 experts (4 chosen, 4d/8 wide each,
+    and a shared expert) that run twice, then another attention layer; a pair table of 4,093 buckets."""
+    H = d // 128
+    lin = dict(type="lightning", mixer=dict(heads=H, dim=128, vdim=128, decay=[1.0 - 2.0 ** (-5 - 3 * h / max(1, H - 1)) for h in range(H)]))
+    att = dict(type="attention", mixer=dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, scale=0.09, rot=dict(base=10000.0, dims=64)))
+    experts = dict(kind="moe", router=dict(experts=16, top=4), expert=dict(ff=d // 2, limit=7.0), shared=dict(ff=d // 2, limit=7.0))
+    return dict(architecture="Pibalorn", vocab=32000, width=d, norm=dict(eps=1e-5),
+                embedding=dict(scale=float(d) ** 0.5, bigram=dict(buckets=4093, mul_prev=127, mul_cur=17)),
+                loop=dict(start=1, stop=3, times=2),
+                layers=[dict(lin, mlp=dict(kind="dense", ff=(8 * d // 3 + 255) // 256 * 256, limit=7.0)), dict(att, mlp=experts), dict(lin, mlp=experts),
+                        dict(att, mlp=experts)])
+
+
 def roletar_workload(args) -> int:
-    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at context 2,048) of the Roletar design beside the
+    return design_workload(args, "roletar")
+
+
+def design_workload(args, design: str) -> int:
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at context 2,048) of a design (Roletar, Pibalorn) beside the
     Yi architecture at equal width and layer count, through ``ModelRunner.step``, timed with CUDA events after warm-up with
     the L2 flushed before every timed step; then every launcher's share of one such step, with the fraction of the measured
     peaks that the design's own kernels and their Yi counterparts reach."""
@@ -415,7 +438,8 @@ def roletar_workload(args) -> int:
     gen = torch.Generator().manual_seed(1)
     clocks = ClockSampler()
     clocks.start()
-    out = {"workload": "roletar", "metric": "prefill tok/s and decode tok/s (Roletar beside Yi at equal width and layer runs, bf16)",
+    Design = design.capitalize()
+    out = {"workload": design, "metric": f"prefill tok/s and decode tok/s ({Design} beside Yi at equal width and layer runs, bf16)",
            "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic token ids, random weights",
            "steps": args.steps, "warmup": args.warmup, "peaks": pk, "sizes": {}}
 
@@ -482,7 +506,7 @@ def roletar_workload(args) -> int:
 
     launches = 0
     for d in args.width:
-        rc = roletar_config(d)
+        rc = roletar_config(d) if design == "roletar" else pibalorn_config(d)
         runs = 6
         yc = yi_like_config(d, runs)
         a, b = measure(rc, rc["vocab"]), measure(yc, yc["vocab_size"])
@@ -500,6 +524,20 @@ def roletar_workload(args) -> int:
             "gemm_nt_plain_batched": (0, 2 * T * H * (128 * 256 + 256 * 128) * 4),
             "attention_rows_mma": (0, 4 * (2 * H * (320 + 256) * T * (T + 1) // 2) + 2 * H * 256 * (1024 * T - 1024 * 1023 // 2)),
         }
+        if design == "pibalorn":
+            G, E, top, F = max(1, H // 4), 16, 4, d // 2
+            n_lin, n_att, n_moe = 3, 3, 5          # runs of a linear-attention layer, of an attention layer, of a mixture
+            work = {
+                "residual_norm": ((2 * d * 4 + 3 * d * 2) * T * runs, 0),
+                "embedding_pair": ((2 * d * 2 + 2 * d * 4) * T, 0),
+                "glu_clamped": (3 * (((8 * d // 3 + 255) // 256 * 256) + n_moe * F) * 2 * T, 0),
+                "rows_append_unit": ((2 * H + 3 * G) * 128 * 2 * T * n_att, 0),
+                "gated_rms_norm": ((H * 128 * 4 + 2 * H * 128 * 2) * T * n_lin, 0),
+                "experts_combine": ((top * d * 4 + 2 * d * 2) * T * n_moe, 0),
+                "decay_attention": (0, 2 * T * H * (2 * 128 * 128 + 16 * (128 + 128)) * n_lin),
+                "experts_gemm": (0, 2 * T * top * 3 * d * F * n_moe),
+                "attention_rows_mma": (0, 4 * 128 * H * (T * (T + 1) // 2) * n_att),
+            }
         yi_work = {
             "rms_norm": (4 * d * 2 * T * (2 * runs) , 0),
             "silu_mul": (3 * yc["intermediate_size"] * 2 * T * runs, 0),
@@ -522,7 +560,7 @@ def roletar_workload(args) -> int:
                 rows[name] = row
             return rows
         out["sizes"][str(d)] = {
-            "roletar": {"prefill_tok_s": T / a["prefill_ms"] * 1e3, "prefill_ms": a["prefill_ms"], "decode_tok_s": B / a["decode_ms"] * 1e3,
+            design: {"prefill_tok_s": T / a["prefill_ms"] * 1e3, "prefill_ms": a["prefill_ms"], "decode_tok_s": B / a["decode_ms"] * 1e3,
                         "decode_ms": a["decode_ms"], "decode_graph_ms": a["decode_graph_ms"], "launches_per_decode_step": a["launches_per_decode_step"],
                         "prefill_launchers": fractions(a["prefill_launchers"], work),
                         "decode_launchers": fractions(a["decode_launchers"], {})},
@@ -533,9 +571,9 @@ def roletar_workload(args) -> int:
             "config": {"width": d, "layer_runs": runs, "prefill_tokens": T, "decode_batch": B, "decode_context": CTX,
                        "l2": "flushed before every timed step"}}
     first = out["sizes"][str(args.width[0])]
-    out.update(value=first["roletar"]["prefill_tok_s"], ms_per_step=first["roletar"]["prefill_ms"], vs_baseline=None,
+    out.update(value=first[design]["prefill_tok_s"], ms_per_step=first[design]["prefill_ms"], vs_baseline=None,
                gpu_launches=launches, clocks=clocks.stop(),
-               config={"model": f"Roletar, width {args.width[0]}, 6 layer runs", "global_batch": 1, "seq_len": T, "parallelism": "single GPU"})
+               config={"model": f"{Design}, width {args.width[0]}, 6 layer runs", "global_batch": 1, "seq_len": T, "parallelism": "single GPU"})
     print(json.dumps(out))
     return 0
 
@@ -555,8 +593,8 @@ def main() -> int:
     ap.add_argument("--enable_selective_cache", action="store_true", help="DELTA on (not the default run)")
     ap.add_argument("--full_cache_layers", nargs="+", type=int, default=[0, 1, 2, 14, 22])
     ap.add_argument("--subset_cache_size", type=int, default=64)
-    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown", "long-prompt", "roletar"], default="decode")
-    ap.add_argument("--width", type=int, nargs="+", default=[2048, 4096], help="--workload roletar: the model widths that are measured")
+    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown", "long-prompt", "roletar", "pibalorn"], default="decode")
+    ap.add_argument("--width", type=int, nargs="+", default=[2048, 4096], help="--workload roletar / pibalorn: the model widths that are measured")
     ap.add_argument("--generate", type=int, default=None, help="tokens generated per request in the other workloads (default: what the workload names)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -566,8 +604,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    if args.workload == "roletar":
-        return roletar_workload(args)
+    if args.workload in ("roletar", "pibalorn"):
+        return design_workload(args, args.workload)
     if args.workload != "decode":
         return other_workload(args)
 

@@ -1,7 +1,7 @@
 // A mixture of small feed-forward experts, and the gated activation its experts and dense layers share.
 //
 //   glu_clamped     y = g' * sigmoid(alpha g') * (u' + shift),  g' = min(g, limit), u' = clamp(u, -limit, limit)
-//                   from rows [g (F) | u (F)] (limit <= 0: nothing is clamped);
+//                   from rows [g (F) | u (F)] (limit < 0: nothing is clamped);
 //   router_topk     per token the `top` largest of E router logits (32 bit; the lowest index among equals) and the
 //                   softmax over the chosen logits only;
 //   experts_align   sorts the (token, choice) slots by expert into tiles of TILE_M rows that each belong to one expert
@@ -26,7 +26,7 @@ constexpr int MAX_TOP = 32;
 constexpr int MAX_EXPERTS = 1024;
 
 __device__ __forceinline__ float glu_value(float g, float u, float limit, float alpha, float shift) {
-  if (limit > 0.f) {
+  if (limit >= 0.f) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
   }

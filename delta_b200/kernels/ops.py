@@ -706,9 +706,9 @@ def gated_rms_norm(o, gate_ptr, gate_stride, weight, out, eps):
 
 # ---- gated feed-forwards and a mixture of experts ---------------------------------------------------------------
 
-def glu_clamped(gate_up, out, limit=0.0, alpha=1.702, shift=1.0):
+def glu_clamped(gate_up, out, limit=-1.0, alpha=1.702, shift=1.0):
     """out = g' * sigmoid(alpha g') * (u' + shift) from rows [g | u], g' = min(g, limit), u' = clamp(u, -limit, limit)
-    (``limit`` 0: unclamped)."""
+    (``limit`` negative: unclamped)."""
     rows, F2 = gate_up.shape
     _l.check(_l.load().dk_glu_clamped(_ptr(gate_up, "gate_up"), _ptr(out, "out", gate_up.dtype), rows, F2 // 2, float(limit), float(alpha),
                                       float(shift), dtype_code(gate_up.dtype), _stream()), "glu_clamped")
@@ -732,7 +732,7 @@ def experts_align(choice, experts, sorted_slots, tile_expert):
                                         _ptr(tile_expert, "tile_expert", torch.int32), tile_expert.numel(), _stream()), "experts_align")
 
 
-def experts_gemm(a, w, out, sorted_slots, tile_expert, *, top, n, k, act=False, limit=0.0, alpha=1.702, shift=1.0):
+def experts_gemm(a, w, out, sorted_slots, tile_expert, *, top, n, k, act=False, limit=-1.0, alpha=1.702, shift=1.0):
     """For every tile of rows its expert's product (see ``csrc/experts.cu``); ``w`` is [E, n (2n with ``act``), k]."""
     _l.check(_l.load().dk_experts_gemm(_ptr(a, "a"), _ptr(w, "w", a.dtype), _ptr(out, "out"), _ptr(sorted_slots, "sorted_slots", torch.int32),
                                        _ptr(tile_expert, "tile_expert", torch.int32), tile_expert.numel(), int(top), int(n), int(k),

@@ -94,9 +94,10 @@ class Model:
         return f"run{cache_id}.{name}"
 
     def has_run_state(self) -> bool:
-        """True when some layer carries a recurrent state from step to step: a step that ran cannot be run again
-        from the same start, unlike one that only appended keys and values."""
-        return any(self.blocks[e.layer].run_state_specs() for e in self.order)
+        """True when some layer carries a recurrent state from step to step, or the stream keeps something of a request's
+        last step (its previous token): a step that ran cannot be run again from the same start, unlike one that only
+        appended keys and values."""
+        return any(self.blocks[e.layer].run_state_specs() for e in self.order) or bool(self.stream.state_specs())
 
     # ---- a step -------------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor:

@@ -46,11 +46,11 @@ def _feed_forward(cfg: PibalornConfig, i: int) -> Optional[PartSpec]:
         return None
     glu = dict(alpha=GLU_ALPHA, shift=GLU_SHIFT)
     if mlp["kind"] == "dense":
-        return PartSpec("clamped_glu", dict(prefix=pre, width=d, intermediate=mlp["ff"], limit=mlp.get("limit", 0.0), **glu), "feed_forward")
+        return PartSpec("clamped_glu", dict(prefix=pre, width=d, intermediate=mlp["ff"], limit=mlp.get("limit"), **glu), "feed_forward")
     shared = mlp.get("shared")
     return PartSpec("experts", dict(prefix=pre, width=d, experts=mlp["router"]["experts"], top=mlp["router"]["top"],
-                                    intermediate=mlp["expert"]["ff"], limit=mlp["expert"].get("limit", 0.0),
-                                    shared=dict(intermediate=shared["ff"], limit=shared.get("limit", 0.0)) if shared else None, **glu),
+                                    intermediate=mlp["expert"]["ff"], limit=mlp["expert"].get("limit"),
+                                    shared=dict(intermediate=shared["ff"], limit=shared.get("limit")) if shared else None, **glu),
                     "feed_forward")
 
 

@@ -26,16 +26,18 @@ class Experts(FeedForward):
     """Tensor names under ``prefix``: ``router`` [E, d]; ``e<i>.gate|up`` [F, d], ``e<i>.down`` [d, F]; with a shared expert
     ``shared.gate|up|down`` and ``shared.sg`` [1, d]."""
 
-    def __init__(self, prefix: str, width: int, experts: int, top: int, intermediate: int, limit: float = 0.0, alpha: float = 1.702,
+    def __init__(self, prefix: str, width: int, experts: int, top: int, intermediate: int, limit=None, alpha: float = 1.702,
                  shift: float = 1.0, shared: Optional[dict] = None):
         self.prefix, self.width = prefix, int(width)
         self.experts, self.top, self.intermediate = int(experts), int(top), int(intermediate)
         if not (1 <= self.top <= self.experts):
             raise ValueError(f"{self.top} of {self.experts} experts cannot be chosen")
-        self.limit, self.alpha, self.shift = float(limit or 0.0), float(alpha), float(shift)
+        if limit is not None and float(limit) < 0:
+            raise ValueError(f"a clamp at {limit} is no limit")
+        self.limit, self.alpha, self.shift = (-1.0 if limit is None else float(limit)), float(alpha), float(shift)
         self.shared = None
         if shared:
-            self.shared = ClampedGLU(prefix + "shared.", width, int(shared["intermediate"]), limit=shared.get("limit", 0.0),
+            self.shared = ClampedGLU(prefix + "shared.", width, int(shared["intermediate"]), limit=shared.get("limit"),
                                      alpha=shared.get("alpha", alpha), shift=shared.get("shift", shift))
         self.w_router = self.w1 = self.w2 = None
 

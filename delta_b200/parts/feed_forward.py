@@ -71,11 +71,13 @@ class DenseMLP(FeedForward):
 @FEED_FORWARDS.register("clamped_glu")
 class ClampedGLU(FeedForward):
     """down( g' * sigmoid(alpha g') * (u' + shift) ) with g' = min(gate x, limit) and u' = clamp(up x, -limit, limit)
-    (``limit`` 0: unclamped).  Tensor names: ``<prefix>gate``, ``<prefix>up`` [I, d] and ``<prefix>down`` [d, I]."""
+    (``limit`` None: unclamped).  Tensor names: ``<prefix>gate``, ``<prefix>up`` [I, d] and ``<prefix>down`` [d, I]."""
 
-    def __init__(self, prefix: str, width: int, intermediate: int, limit: float = 0.0, alpha: float = 1.702, shift: float = 1.0):
+    def __init__(self, prefix: str, width: int, intermediate: int, limit=None, alpha: float = 1.702, shift: float = 1.0):
         self.prefix, self.width, self.intermediate = prefix, int(width), int(intermediate)
-        self.limit, self.alpha, self.shift = float(limit or 0.0), float(alpha), float(shift)
+        if limit is not None and float(limit) < 0:
+            raise ValueError(f"a clamp at {limit} is no limit")
+        self.limit, self.alpha, self.shift = (-1.0 if limit is None else float(limit)), float(alpha), float(shift)
         self.w_gate_up = self.w_down = None
 
     def tensor_specs(self):

@@ -58,8 +58,8 @@ def layer_norm(x, w, eps):
 def embed_tokens(cfg, W, tokens):
     """Token rows times the scale, plus a row of the bigram table picked by a hash of (previous token, token); the
     first token of a sequence takes the table's last row."""
-    e = cfg["embedding"]
-    x = W["embed"].to(F)[tokens] * float(e["scale"])
+    e = cfg.get("embedding") or {}
+    x = W["embed"].to(F)[tokens] * float(e.get("scale", 1.0))
     bg = e.get("bigram")
     if bg:
         n = int(bg["buckets"])
@@ -134,8 +134,9 @@ def lightning(m, W, p, h, eps):
 # ------------------------------------------------------------ feed-forward
 
 def glu(W, p, h, limit):
-    g = torch.clamp(lin(h, W[p + "gate"]), max=float(limit))
-    u = torch.clamp(lin(h, W[p + "up"]), min=-float(limit), max=float(limit))
+    g, u = lin(h, W[p + "gate"]), lin(h, W[p + "up"])
+    if limit is not None:
+        g, u = torch.clamp(g, max=float(limit)), torch.clamp(u, min=-float(limit), max=float(limit))
     y = rnd(g * torch.sigmoid(1.702 * g) * (u + 1.0))
     return lin(y, W[p + "down"])
 
@@ -150,16 +151,16 @@ def experts(mlp, W, p, h):
     for t in range(T):
         for j in range(top):
             e = int(idx[t, j])
-            out[t] += w[t, j] * glu(W, f"{p}e{e}.", h[t:t + 1], mlp["expert"]["limit"])[0]
+            out[t] += w[t, j] * glu(W, f"{p}e{e}.", h[t:t + 1], mlp["expert"].get("limit"))[0]
     if mlp.get("shared"):
         gate = torch.sigmoid(h @ W[p + "shared.sg"].to(F).T)
-        out = out + gate * glu(W, p + "shared.", h, mlp["shared"]["limit"])
+        out = out + gate * glu(W, p + "shared.", h, mlp["shared"].get("limit"))
     return rnd(out)
 
 
 def feed_forward(mlp, W, p, h):
     if mlp["kind"] == "dense":
-        return glu(W, p, h, mlp["limit"])
+        return glu(W, p, h, mlp.get("limit"))
     if mlp["kind"] == "moe":
         return experts(mlp, W, p, h)
     raise ValueError(mlp["kind"])
