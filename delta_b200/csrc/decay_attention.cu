@@ -99,6 +99,216 @@ decay_attention_kernel(const T* __restrict__ src, int src_stride, int q_off, int
   }
 }
 
+// ---- long portions: the chunks of a row run in parallel --------------------------------------------------------------
+// The recurrence is linear in the state, so with U_c = sum_s lambda^(n-1-s) k_s v_s^T of chunk c taken alone:
+//   1. decay_chunk_state: U_c for every chunk of every row, in parallel;
+//   2. decay_chunk_scan:  S_c = lambda^n S_(c-1) + U_c along a row, element by element; the state BEFORE chunk c takes the
+//                         place of U_c, the last one goes to the request's slot;
+//   3. decay_chunk_out:   o_t = lambda^(t+1) S^T q_t + sum_{s<=t} lambda^(t-s) (q_t . k_s) v_s  for every chunk, in parallel.
+// Threads hold 4 x 4 tiles of outputs in registers and read shared memory sixteen bytes at a time.
+constexpr int PC = 32;             // tokens of a chunk on this path
+constexpr int PCP = PC + 4;        // padded row of the transposed tiles
+
+__device__ __forceinline__ int up4(int n) { return (n + 3) & ~3; }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+decay_chunk_state_kernel(const T* __restrict__ src, int src_stride, int k_off, int v_off, int act, const double* __restrict__ decays,
+                         float* __restrict__ U, const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
+                         const int* __restrict__ chunk_base, int H, int dk, int dv, int dvs) {
+  extern __shared__ __align__(16) float sm[];
+  const int row = blockIdx.y / H, h = blockIdx.y % H, j0 = blockIdx.z * dvs;
+  const int jn = min(dvs, dv - j0), c0 = blockIdx.x * PC, n_new = row_q_len[row];
+  if (c0 >= n_new || jn <= 0) return;
+  const int n = min(PC, n_new - c0), t0 = row_q_start[row] + c0;
+  const int dkp = up4(dk), dvp = up4(dvs), tid = threadIdx.x;
+  float* Kd = sm;                    // [PC][dkp]: keys times lambda^(n-1-s)
+  float* V = Kd + PC * dkp;          // [PC][dvp]
+  float* pw = V + PC * dvp;          // [PC + 1]
+  if (tid <= PC) pw[tid] = (float)pow(decays[h], (double)tid);
+  __syncthreads();
+  for (int idx = tid; idx < PC * dkp; idx += 256) {
+    const int s = idx / dkp, i = idx - s * dkp;
+    float v = 0.f;
+    if (s < n && i < dk) {
+      v = to_f32<T>(src[(size_t)(t0 + s) * src_stride + k_off + (size_t)h * dk + i]);
+      if (act) v = act_silu(v);
+      v *= pw[n - 1 - s];
+    }
+    Kd[idx] = v;
+  }
+  for (int idx = tid; idx < PC * dvp; idx += 256) {
+    const int s = idx / dvp, j = idx - s * dvp;
+    float v = 0.f;
+    if (s < n && j < jn) {
+      v = to_f32<T>(src[(size_t)(t0 + s) * src_stride + v_off + (size_t)h * dv + j0 + j]);
+      if (act) v = act_silu(v);
+    }
+    V[idx] = v;
+  }
+  __syncthreads();
+  float* Uc = U + ((size_t)(chunk_base[row] + blockIdx.x) * H + h) * dk * dv;
+  const int tiles_j = dvp / 4, tiles = (dkp / 4) * tiles_j;
+  for (int tile = tid; tile < tiles; tile += 256) {
+    const int ti = tile / tiles_j, tj = tile - ti * tiles_j;
+    float acc[4][4] = {};
+    for (int s = 0; s < n; ++s) {
+      const float4 a = *reinterpret_cast<const float4*>(Kd + s * dkp + 4 * ti);
+      const float4 b = *reinterpret_cast<const float4*>(V + s * dvp + 4 * tj);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int x = 0; x < 4; ++x)
+#pragma unroll
+        for (int y = 0; y < 4; ++y) acc[x][y] = fmaf(av[x], bv[y], acc[x][y]);
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y)
+        if (4 * ti + x < dk && 4 * tj + y < jn) Uc[(size_t)(4 * ti + x) * dv + j0 + 4 * tj + y] = acc[x][y];
+  }
+}
+
+__global__ void decay_chunk_scan_kernel(float* __restrict__ U, float* __restrict__ state, const double* __restrict__ decays,
+                                        const int* __restrict__ row_slot, const int* __restrict__ row_q_len,
+                                        const int* __restrict__ chunk_base, int H, int per_head) {
+  const int row = blockIdx.y / H, h = blockIdx.y % H;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n_new = row_q_len[row];
+  if (e >= per_head || n_new <= 0) return;
+  const int chunks = (n_new + PC - 1) / PC;
+  const float lam_full = (float)pow(decays[h], (double)PC), lam_last = (float)pow(decays[h], (double)(n_new - (chunks - 1) * PC));
+  float* st = state + ((size_t)row_slot[row] * H + h) * per_head + e;
+  float* u = U + ((size_t)chunk_base[row] * H + h) * per_head + e;
+  const size_t step = (size_t)H * per_head;
+  float S = *st;
+  float next = u[0];
+  for (int c = 0; c < chunks; ++c) {
+    const float cur = next;
+    if (c + 1 < chunks) next = u[(size_t)(c + 1) * step];
+    u[(size_t)c * step] = S;
+    S = fmaf(c + 1 < chunks ? lam_full : lam_last, S, cur);
+  }
+  *st = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+decay_chunk_out_kernel(const T* __restrict__ src, int src_stride, int q_off, int k_off, int v_off, int act,
+                       const double* __restrict__ decays, const float* __restrict__ U, float* __restrict__ out,
+                       const int* __restrict__ row_q_start, const int* __restrict__ row_q_len, const int* __restrict__ chunk_base,
+                       int H, int dk, int dv, int dvs) {
+  extern __shared__ __align__(16) float sm[];
+  const int row = blockIdx.y / H, h = blockIdx.y % H, j0 = blockIdx.z * dvs;
+  const int jn = min(dvs, dv - j0), c0 = blockIdx.x * PC, n_new = row_q_len[row];
+  if (c0 >= n_new || jn <= 0) return;
+  const int n = min(PC, n_new - c0), t0 = row_q_start[row] + c0;
+  const int dkp = up4(dk), dvp = up4(dvs), tid = threadIdx.x;
+  float* Qt = sm;                    // [dkp][PCP]: queries, transposed
+  float* Kt = Qt + dkp * PCP;        // [dkp][PCP]
+  float* S = Kt + dkp * PCP;         // [dkp][dvp]: the state before the chunk
+  float* V = S + dkp * dvp;          // [PC][dvp]
+  float* At = V + PC * dvp;          // [PC][PCP]: At[s][t] = lambda^(t-s) q_t . k_s for s <= t, else 0
+  float* pw = At + PC * PCP;         // [PC + 1]
+  if (tid <= PC) pw[tid] = (float)pow(decays[h], (double)tid);
+  for (int idx = tid; idx < dkp * PC; idx += 128) {
+    const int t = idx / dkp, i = idx - t * dkp;
+    float qv = 0.f, kv = 0.f;
+    if (t < n && i < dk) {
+      const T* p = src + (size_t)(t0 + t) * src_stride + (size_t)h * dk + i;
+      qv = to_f32<T>(p[q_off]);
+      kv = to_f32<T>(p[k_off]);
+      if (act) {
+        qv = act_silu(qv);
+        kv = act_silu(kv);
+      }
+    }
+    Qt[i * PCP + t] = qv;
+    Kt[i * PCP + t] = kv;
+  }
+  const float* Sc = U + ((size_t)(chunk_base[row] + blockIdx.x) * H + h) * dk * dv;
+  for (int idx = tid; idx < dkp * dvp; idx += 128) {
+    const int i = idx / dvp, j = idx - i * dvp;
+    S[idx] = (i < dk && j < jn) ? Sc[(size_t)i * dv + j0 + j] : 0.f;
+  }
+  for (int idx = tid; idx < PC * dvp; idx += 128) {
+    const int s = idx / dvp, j = idx - s * dvp;
+    float v = 0.f;
+    if (s < n && j < jn) {
+      v = to_f32<T>(src[(size_t)(t0 + s) * src_stride + v_off + (size_t)h * dv + j0 + j]);
+      if (act) v = act_silu(v);
+    }
+    V[idx] = v;
+  }
+  __syncthreads();
+  // scores of the chunk: tiles on and below the diagonal
+  for (int tile = tid; tile < (PC / 4) * (PC / 4); tile += 128) {
+    const int tt = tile / (PC / 4), ts = tile - tt * (PC / 4);
+    float acc[4][4] = {};
+    if (ts <= tt) {
+      for (int i = 0; i < dk; ++i) {
+        const float4 a = *reinterpret_cast<const float4*>(Qt + i * PCP + 4 * tt);
+        const float4 b = *reinterpret_cast<const float4*>(Kt + i * PCP + 4 * ts);
+        const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+          for (int y = 0; y < 4; ++y) acc[x][y] = fmaf(av[x], bv[y], acc[x][y]);
+      }
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y) {
+        const int t = 4 * tt + x, s2 = 4 * ts + y;
+        At[s2 * PCP + t] = (s2 <= t) ? acc[x][y] * pw[t - s2] : 0.f;
+      }
+  }
+  __syncthreads();
+  const int tiles_j = dvp / 4;
+  for (int tile = tid; tile < (PC / 4) * tiles_j; tile += 128) {
+    const int tt = tile / tiles_j, tj = tile - tt * tiles_j;
+    if (4 * tt >= n) continue;
+    float far[4][4] = {}, near[4][4] = {};
+    for (int i = 0; i < dk; ++i) {
+      const float4 a = *reinterpret_cast<const float4*>(Qt + i * PCP + 4 * tt);
+      const float4 b = *reinterpret_cast<const float4*>(S + i * dvp + 4 * tj);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int x = 0; x < 4; ++x)
+#pragma unroll
+        for (int y = 0; y < 4; ++y) far[x][y] = fmaf(av[x], bv[y], far[x][y]);
+    }
+    const int s_end = min(n, 4 * tt + 4);
+    for (int s2 = 0; s2 < s_end; ++s2) {
+      const float4 a = *reinterpret_cast<const float4*>(At + s2 * PCP + 4 * tt);
+      const float4 b = *reinterpret_cast<const float4*>(V + s2 * dvp + 4 * tj);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int x = 0; x < 4; ++x)
+#pragma unroll
+        for (int y = 0; y < 4; ++y) near[x][y] = fmaf(av[x], bv[y], near[x][y]);
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y) {
+        const int t = 4 * tt + x, j = 4 * tj + y;
+        if (t < n && j < jn) out[(size_t)(t0 + t) * ((size_t)H * dv) + (size_t)h * dv + j0 + j] = fmaf(pw[t + 1], far[x][y], near[x][y]);
+      }
+  }
+}
+
+size_t chunk_out_smem(int dk, int dvs) {
+  const int dkp = (dk + 3) & ~3, dvp = (dvs + 3) & ~3;
+  return ((size_t)2 * dkp * PCP + (size_t)dkp * dvp + (size_t)PC * dvp + (size_t)PC * PCP + PC + 1) * sizeof(float);
+}
+size_t chunk_state_smem(int dk, int dvs) {
+  const int dkp = (dk + 3) & ~3, dvp = (dvs + 3) & ~3;
+  return ((size_t)PC * dkp + (size_t)PC * dvp + PC + 1) * sizeof(float);
+}
+int chunk_slice(int dv) { return dv <= 64 ? dv : 64; }
+
 template <typename T>
 __global__ void gated_rms_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
                                       const float* __restrict__ w, T* __restrict__ out, int n, float eps) {
@@ -166,4 +376,46 @@ extern "C" int dk_gated_rms_norm(const float* o, const void* gate, int gate_stri
     gated_rms_norm_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(o, (const __nv_bfloat16*)gate, gate_stride, w, (__nv_bfloat16*)out, n, eps);
   else DK_REQUIRE(false, "gated_rms_norm: unknown dtype %d", dtype);
   return dk_check_launch("gated_rms_norm");
+}
+
+// The chunk-parallel path.  `chunk_base` [rows]: the number of chunks (of dk_decay_attention_chunk() tokens) of all rows
+// before this one; `U` holds total chunks x H x dk x dv floats; `max_chunks`: the most chunks of any row.
+extern "C" int dk_decay_attention_chunk() { return PC; }
+
+extern "C" int dk_decay_attention_chunked_supported(int dk, int dv) {
+  return chunk_out_smem(dk, chunk_slice(dv)) <= SMEM_LIMIT && chunk_state_smem(dk, chunk_slice(dv)) <= SMEM_LIMIT;
+}
+
+extern "C" int dk_decay_attention_chunked(const void* src, int src_stride, int q_off, int k_off, int v_off, int act, const double* decays,
+                                          float* state, float* out, float* U, const int* row_slot, const int* row_q_start,
+                                          const int* row_q_len, const int* chunk_base, int rows, int max_chunks, int H, int dk, int dv,
+                                          int dtype, cudaStream_t stream) {
+  if (rows == 0 || max_chunks == 0) return 0;
+  DK_REQUIRE(rows > 0 && max_chunks > 0 && H > 0 && dk > 0 && dv > 0, "decay_attention_chunked: bad sizes rows=%d chunks=%d H=%d dk=%d dv=%d", rows,
+             max_chunks, H, dk, dv);
+  DK_REQUIRE((long long)rows * H <= 65535, "decay_attention_chunked: %d rows of %d heads are above the grid's limit", rows, H);
+  const int dvs = chunk_slice(dv);
+  const size_t sm1 = chunk_state_smem(dk, dvs), sm3 = chunk_out_smem(dk, dvs);
+  DK_REQUIRE(sm1 <= SMEM_LIMIT && sm3 <= SMEM_LIMIT, "decay_attention_chunked: heads of %d x %d do not fit the shared memory", dk, dv);
+  const dim3 grid(max_chunks, rows * H, (dv + dvs - 1) / dvs);
+  const int per_head = dk * dv;
+  const dim3 scan_grid((per_head + 255) / 256, rows * H);
+#define LAUNCH(T)                                                                                                                       \
+  do {                                                                                                                                  \
+    if (cudaFuncSetAttribute(decay_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1) != cudaSuccess ||     \
+        cudaFuncSetAttribute(decay_chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3) != cudaSuccess) {       \
+      cudaGetLastError();                                                                                                               \
+      DK_REQUIRE(false, "decay_attention_chunked: shared memory was not granted");                                                      \
+    }                                                                                                                                   \
+    decay_chunk_state_kernel<T><<<grid, 256, sm1, stream>>>((const T*)src, src_stride, k_off, v_off, act, decays, U, row_q_start,     \
+                                                            row_q_len, chunk_base, H, dk, dv, dvs);                                   \
+    decay_chunk_scan_kernel<<<scan_grid, 256, 0, stream>>>(U, state, decays, row_slot, row_q_len, chunk_base, H, per_head);            \
+    decay_chunk_out_kernel<T><<<grid, 128, sm3, stream>>>((const T*)src, src_stride, q_off, k_off, v_off, act, decays, U, out,         \
+                                                          row_q_start, row_q_len, chunk_base, H, dk, dv, dvs);                         \
+  } while (0)
+  if (dtype == DK_F32) LAUNCH(float);
+  else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
+  else DK_REQUIRE(false, "decay_attention_chunked: unknown dtype %d", dtype);
+#undef LAUNCH
+  return dk_check_launch("decay_attention_chunked");
 }

@@ -2,8 +2,9 @@
 //
 //   glu_clamped     y = g' * sigmoid(alpha g') * (u' + shift),  g' = min(g, limit), u' = clamp(u, -limit, limit)
 //                   from rows [g (F) | u (F)] (limit < 0: nothing is clamped);
-//   router_topk     per token the `top` largest of E router logits (32 bit; the lowest index among equals) and the
-//                   softmax over the chosen logits only;
+//   router          per token the router's logits z = W x in 32 bit, the `top` largest of the E experts' logits (the lowest
+//                   index among equals) and the softmax over the chosen logits only (router_topk: the choice alone, from
+//                   logits that are there already);
 //   experts_align   sorts the (token, choice) slots by expert into tiles of TILE_M rows that each belong to one expert
 //                   (every expert's rows padded to whole tiles with -1), so that the products run as one launch and
 //                   nothing about the routing is read on the host;
@@ -14,11 +15,13 @@
 //   experts_combine out[t] = sum_j weight[t][j] * z[t*top + j]  (+ sigmoid(gate logit of t) * shared[t]), summed in 32 bit in
 //                   the order of the choices, so the result does not depend on what else is in the batch.
 //
-// The products here run on the FMA units with 32-bit accumulation for both element types.
+// The products run on the tensor cores for bfloat16 (warp-level MMA, 32-bit accumulation) and on the FMA units in 32 bit
+// (and for bfloat16 rows whose length is no multiple of 8).
 #include "common.cuh"
+#include "mma_helpers.cuh"
 
 namespace {
-constexpr int TILE_M = 32;
+constexpr int TILE_M = 64;
 constexpr int TILE_N = 64;
 constexpr int TILE_K = 16;
 constexpr int GEMM_THREADS = 256;
@@ -44,39 +47,133 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ y, 
   }
 }
 
-__global__ void router_topk_kernel(const float* __restrict__ logits, int ld, int* __restrict__ choice, float* __restrict__ weight, int T_,
-                                   int E, int top) {
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= T_) return;
-  const float* z = logits + (size_t)t * ld;
-  int picked[MAX_TOP];
-  float val[MAX_TOP];
+// The `top` largest of z[0..E) (the lowest index among equals) and the softmax over them, by one warp.  z is the warp's own
+// copy (shared memory) and is used up: a chosen entry is set to -inf.
+__device__ void pick_top(float* z, int E, int top, int* __restrict__ choice, float* __restrict__ weight, int lane) {
+  float largest = 0.f, sum = 0.f, my_weight = 0.f;
+  int my_choice = -1;
   for (int j = 0; j < top; ++j) {
-    int best = -1;
-    float bv = 0.f;
-    for (int e = 0; e < E; ++e) {
-      bool taken = false;
-      for (int q = 0; q < j; ++q) taken |= picked[q] == e;
-      if (taken) continue;
+    float bv = -INFINITY;
+    int be = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
       const float v = z[e];
-      if (best < 0 || v > bv) {
-        best = e;
+      if (v > bv) {
         bv = v;
+        be = e;
       }
     }
-    picked[j] = best;
-    val[j] = bv;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ov > bv || (ov == bv && oe < be)) {
+        bv = ov;
+        be = oe;
+      }
+    }
+    if (j == 0) largest = bv;
+    const float ex = expf(bv - largest);
+    sum += ex;
+    if (lane == j) {
+      my_weight = ex;
+      my_choice = be < E ? be : -1;
+    }
+    if (lane == 0 && be < E) z[be] = -INFINITY;
+    __syncwarp();
   }
-  float sum = 0.f;
-  const float largest = val[0];
-  for (int j = 0; j < top; ++j) {
-    val[j] = expf(val[j] - largest);
-    sum += val[j];
+  if (lane < top) {
+    choice[lane] = my_choice;
+    weight[lane] = my_weight / sum;
   }
-  for (int j = 0; j < top; ++j) {
-    choice[(size_t)t * top + j] = picked[j];
-    weight[(size_t)t * top + j] = val[j] / sum;
+}
+
+constexpr int ROUTER_WARPS = 8;
+
+// One warp per token; the logits are copied to the warp's shared memory first.
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+router_topk_kernel(const float* __restrict__ logits, int ld, int* __restrict__ choice, float* __restrict__ weight, int T_, int E, int top) {
+  extern __shared__ float zs[];      // [warps][E]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * ROUTER_WARPS + warp;
+  if (t >= T_) return;
+  float* z = zs + (size_t)warp * E;
+  for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)t * ld + e];
+  __syncwarp();
+  pick_top(z, E, top, choice + (size_t)t * top, weight + (size_t)t * top, lane);
+}
+
+// The router's product and its choice in one kernel: the n_rows logits z = W x of a token in 32 bit (the first E are the
+// experts'; further rows, such as a gate's, are only stored), then the choice.  A block takes `tpb` tokens (1, 2, 4 or 8); the
+// 8 / tpb warps of a token share its rows in groups of ROUTER_ROWS, so that a step of few tokens still has many loads under way.
+constexpr int ROUTER_ROWS = 8;      // rows of the matrix whose products a warp has under way at a time
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __low2float(h[i]);
+    v[2 * i + 1] = __high2float(h[i]);
   }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+router_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restrict__ logits, int* __restrict__ choice,
+              float* __restrict__ weight, int T_, int d, int n_rows, int E, int top, int tpb) {
+  extern __shared__ float zs[];      // [tpb][n_rows]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int local = warp % tpb, share = warp / tpb, sharers = ROUTER_WARPS / tpb;
+  const int t = blockIdx.x * tpb + local;
+  const bool live = t < T_;
+  float* z = zs + (size_t)local * n_rows;
+  const T* xr = x + (size_t)(live ? t : 0) * d;
+  for (int r0 = share * ROUTER_ROWS; live && r0 < n_rows; r0 += sharers * ROUTER_ROWS) {
+    float acc[ROUTER_ROWS];
+#pragma unroll
+    for (int q = 0; q < ROUTER_ROWS; ++q) acc[q] = 0.f;
+    if (VEC) {      // d is a multiple of 8 and the rows are 16-byte aligned: eight entries a load
+#pragma unroll 2
+      for (int c = lane * 8; c < d; c += 256) {
+        float xv[8];
+        load8<T>(xr + c, xv);
+#pragma unroll
+        for (int q = 0; q < ROUTER_ROWS; ++q) {
+          if (r0 + q < n_rows) {
+            float wv[8];
+            load8<T>(w + (size_t)(r0 + q) * d + c, wv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[q] = fmaf(xv[i], wv[i], acc[q]);
+          }
+        }
+      }
+    } else {
+      for (int i = lane; i < d; i += 32) {
+        const float xv = to_f32<T>(xr[i]);
+#pragma unroll
+        for (int q = 0; q < ROUTER_ROWS; ++q)
+          if (r0 + q < n_rows) acc[q] = fmaf(xv, to_f32<T>(w[(size_t)(r0 + q) * d + i]), acc[q]);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < ROUTER_ROWS; ++q) {
+      const float v = warp_sum(acc[q]);
+      if (lane == 0 && r0 + q < n_rows) {
+        z[r0 + q] = v;
+        logits[(size_t)t * n_rows + r0 + q] = v;
+      }
+    }
+  }
+  __syncthreads();
+  if (live && share == 0) pick_top(z, E, top, choice + (size_t)t * top, weight + (size_t)t * top, lane);
 }
 
 // One block.  sorted[p] = slot (token * top + choice) or -1; tile_expert[tile] = expert or -1.
@@ -131,12 +228,12 @@ experts_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __re
   }
   __syncthreads();
   const T* We = W + (size_t)e * (ACT ? 2 : 1) * N * K;
-  const int ty = tid / 16, tx = tid % 16;      // rows 2*ty, 2*ty+1; columns tx + 16*c
-  float acc[ACT ? 2 : 1][2][4];
+  const int ty = tid / 16, tx = tid % 16;      // rows 4*ty .. 4*ty+3; columns tx + 16*c
+  float acc[ACT ? 2 : 1][4][4];
 #pragma unroll
   for (int a = 0; a < (ACT ? 2 : 1); ++a)
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
+    for (int r = 0; r < 4; ++r)
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[a][r][c] = 0.f;
   for (int k0 = 0; k0 < K; k0 += TILE_K) {
@@ -154,24 +251,26 @@ experts_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __re
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < TILE_K; ++k) {
-      const float a0 = As[2 * ty][k], a1 = As[2 * ty + 1][k];
+      float a[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) a[r] = As[4 * ty + r][k];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const float w0 = Ws[0][tx + 16 * c][k];
-        acc[0][0][c] = fmaf(a0, w0, acc[0][0][c]);
-        acc[0][1][c] = fmaf(a1, w0, acc[0][1][c]);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) acc[0][r][c] = fmaf(a[r], w0, acc[0][r][c]);
         if (ACT) {
           const float w1 = Ws[ACT ? 1 : 0][tx + 16 * c][k];
-          acc[ACT ? 1 : 0][0][c] = fmaf(a0, w1, acc[ACT ? 1 : 0][0][c]);
-          acc[ACT ? 1 : 0][1][c] = fmaf(a1, w1, acc[ACT ? 1 : 0][1][c]);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) acc[ACT ? 1 : 0][r][c] = fmaf(a[r], w1, acc[ACT ? 1 : 0][r][c]);
         }
       }
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int lr = 2 * ty + r;
+  for (int r = 0; r < 4; ++r) {
+    const int lr = 4 * ty + r;
     const int s = sorted[p0 + lr];
     if (s < 0) continue;
 #pragma unroll
@@ -187,6 +286,138 @@ experts_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __re
       }
     }
   }
+}
+
+// The same products on the tensor cores (warp-level MMA, bfloat16 operands, 32-bit accumulation) for K a multiple of 8:
+// a block of 8 warps takes TILE_M rows x 128 columns, K in steps of 32 through a ring of cp.async stages.  With ACT the 128
+// columns are 64 gate columns and the 64 up columns that belong to them, laid out so that a thread holds both values of an
+// entry and applies the gated activation in registers.
+constexpr int MMA_BN = 128;
+constexpr int MMA_BK = 32;
+constexpr int MMA_LD = MMA_BK + 8;      // padded row: ldmatrix reads eight rows without a bank conflict
+constexpr int MMA_STAGES = 4;
+constexpr int MMA_SMEM = MMA_STAGES * (TILE_M + MMA_BN) * MMA_LD * 2;
+
+template <bool ACT>
+__global__ void __launch_bounds__(256)
+experts_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
+                        const int* __restrict__ sorted, const int* __restrict__ tile_expert, int top, int N, int K, float limit,
+                        float alpha, float shift) {
+  const int tile = blockIdx.y;
+  const int e = tile_expert[tile];
+  if (e < 0) return;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* As = (__nv_bfloat16*)smem_raw;                              // [STAGES][TILE_M][LD]
+  __nv_bfloat16* Bs = As + MMA_STAGES * TILE_M * MMA_LD;                     // [STAGES][BN][LD]
+  __shared__ int src_row[TILE_M];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp >> 2, wn = warp & 3;                                   // 2 x 4 warps: 32 rows x 32 columns each
+  const int cols = ACT ? MMA_BN / 2 : MMA_BN;                                // output columns of the block
+  const int n0 = blockIdx.x * cols, p0 = tile * TILE_M;
+  if (tid < TILE_M) {
+    const int s = sorted[p0 + tid];
+    src_row[tid] = s < 0 ? -1 : (ACT ? s / top : p0 + tid);
+  }
+  __syncthreads();
+  const __nv_bfloat16* We = W + (size_t)e * (ACT ? 2 : 1) * N * K;
+  // what this thread fetches in every stage: one 16-byte piece of A, two of B
+  const int a_r = tid >> 2, a_c = (tid & 3) * 8;
+  const int a_src = src_row[a_r];
+  const __nv_bfloat16* a_ptr = A + (size_t)(a_src < 0 ? 0 : a_src) * K + a_c;
+  const __nv_bfloat16* b_ptr[2];
+  bool b_ok[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = (tid >> 2) + 64 * i;                                       // row of the B tile
+    int n;                                                                   // row of the expert's matrix
+    if (ACT) n = r < 64 ? n0 + r : N + n0 + (r - 64);
+    else n = n0 + r;
+    b_ok[i] = ACT ? (n0 + (r & 63) < N) : (n < N);
+    b_ptr[i] = We + (size_t)(b_ok[i] ? n : 0) * K + a_c;
+  }
+  const int ksteps = (K + MMA_BK - 1) / MMA_BK;
+  auto fetch = [&](int ks) {
+    const int st = ks % MMA_STAGES, k0 = ks * MMA_BK;
+    const bool kin = k0 + a_c < K;
+    cp_async_16(smem_u32(As + ((size_t)st * TILE_M + a_r) * MMA_LD + a_c), kin ? a_ptr + k0 : A, kin && a_src >= 0);
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      cp_async_16(smem_u32(Bs + ((size_t)st * MMA_BN + (tid >> 2) + 64 * i) * MMA_LD + a_c), kin ? b_ptr[i] + k0 : W, kin && b_ok[i]);
+  };
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.f;
+#pragma unroll
+  for (int s = 0; s < MMA_STAGES - 1; ++s) {
+    if (s < ksteps) fetch(s);
+    cp_async_commit();
+  }
+  // n-tiles of this warp in the B tile: ACT: two of the gate half and the two up tiles that belong to them
+  int bn[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) bn[j] = ACT ? ((j >> 1) * 64 + wn * 16 + (j & 1) * 8) : (wn * 32 + j * 8);
+  for (int ks = 0; ks < ksteps; ++ks) {
+    cp_async_wait<MMA_STAGES - 2>();
+    __syncthreads();
+    if (ks + MMA_STAGES - 1 < ksteps) fetch(ks + MMA_STAGES - 1);
+    cp_async_commit();
+    const int st = ks % MMA_STAGES;
+    const __nv_bfloat16* as = As + (size_t)st * TILE_M * MMA_LD;
+    const __nv_bfloat16* bs = Bs + (size_t)st * MMA_BN * MMA_LD;
+#pragma unroll
+    for (int kk = 0; kk < MMA_BK; kk += 16) {
+      uint32_t a[2][4], b[4][2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        ldmatrix_x4(a[i][0], a[i][1], a[i][2], a[i][3],
+                    smem_u32(as + (size_t)(wm * 32 + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * MMA_LD + kk + (lane >> 4) * 8));
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        // two n-tiles that lie 8 rows apart in the B tile: (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+        ldmatrix_x4(b[j][0], b[j][1], b[j + 1][0], b[j + 1][1],
+                    smem_u32(bs + (size_t)(bn[j] + (lane & 7) + (lane >> 4) * 8) * MMA_LD + kk + ((lane >> 3) & 1) * 8));
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], a[i], b[j][0], b[j][1]);
+    }
+  }
+  cp_async_wait<0>();
+  const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int lr = wm * 32 + i * 16 + g + half * 8;
+      const int s = sorted[p0 + lr];
+      if (s < 0) continue;
+      if (ACT) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int n = n0 + wn * 16 + j * 8 + 2 * t4;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            if (n + q >= N) continue;
+            const float gv = __bfloat162float(__float2bfloat16_rn(acc[i][j][half * 2 + q]));
+            const float uv = __bfloat162float(__float2bfloat16_rn(acc[i][j + 2][half * 2 + q]));
+            ((__nv_bfloat16*)out)[(size_t)(p0 + lr) * N + n + q] = __float2bfloat16_rn(glu_value(gv, uv, limit, alpha, shift));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = n0 + wn * 32 + j * 8 + 2 * t4;
+#pragma unroll
+          for (int q = 0; q < 2; ++q)
+            if (n + q < N) ((float*)out)[(size_t)s * N + n + q] = acc[i][j][half * 2 + q];
+        }
+      }
+    }
 }
 
 template <typename T>
@@ -225,8 +456,36 @@ extern "C" int dk_router_topk(const float* logits, int ld, int* choice, float* w
   if (T_ == 0) return 0;
   DK_REQUIRE(T_ > 0 && E > 0 && top > 0 && top <= E && ld >= E, "router_topk: bad sizes T=%d E=%d top=%d ld=%d", T_, E, top, ld);
   DK_REQUIRE(top <= MAX_TOP, "router_topk: %d choices a token are above the %d this kernel takes", top, MAX_TOP);
-  router_topk_kernel<<<(T_ + 63) / 64, 64, 0, stream>>>(logits, ld, choice, weight, T_, E, top);
+  const size_t smem = (size_t)ROUTER_WARPS * E * sizeof(float);
+  DK_REQUIRE(smem <= 48 * 1024, "router_topk: %d logits a token do not fit the shared memory", E);
+  router_topk_kernel<<<(T_ + ROUTER_WARPS - 1) / ROUTER_WARPS, ROUTER_WARPS * 32, smem, stream>>>(logits, ld, choice, weight, T_, E, top);
   return dk_check_launch("router_topk");
+}
+
+extern "C" int dk_router(const void* x, const void* w, float* logits, int* choice, float* weight, int T_, int d, int n_rows, int E, int top,
+                         int dtype, cudaStream_t stream) {
+  if (T_ == 0) return 0;
+  DK_REQUIRE(T_ > 0 && d > 0 && E > 0 && top > 0 && top <= E && n_rows >= E, "router: bad sizes T=%d d=%d E=%d top=%d rows=%d", T_, d, E, top, n_rows);
+  DK_REQUIRE(top <= MAX_TOP, "router: %d choices a token are above the %d this kernel takes", top, MAX_TOP);
+  // few tokens: one token a block, its rows shared by the block's warps; many: eight tokens a block
+  const int groups = (n_rows + ROUTER_ROWS - 1) / ROUTER_ROWS;
+  int tpb = ROUTER_WARPS;
+  while (tpb > 1 && (ROUTER_WARPS / tpb < groups) && (long long)T_ * (ROUTER_WARPS / tpb) < 16LL * dk_sm_count()) tpb /= 2;
+  const size_t smem = (size_t)tpb * n_rows * sizeof(float);
+  DK_REQUIRE(smem <= 48 * 1024, "router: %d logits a token do not fit the shared memory", n_rows);
+  const int blocks = (T_ + tpb - 1) / tpb;
+  const bool vec = d % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0;
+#define LAUNCH(T, V) router_kernel<T, V><<<blocks, ROUTER_WARPS * 32, smem, stream>>>((const T*)x, (const T*)w, logits, choice, weight, T_, d, n_rows, E, top, tpb)
+  if (dtype == DK_F32) {
+    if (vec) LAUNCH(float, true);
+    else LAUNCH(float, false);
+  } else if (dtype == DK_BF16) {
+    if (vec) LAUNCH(__nv_bfloat16, true);
+    else LAUNCH(__nv_bfloat16, false);
+  }
+#undef LAUNCH
+  else DK_REQUIRE(false, "router: unknown dtype %d", dtype);
+  return dk_check_launch("router");
 }
 
 extern "C" int dk_experts_align(const int* choice, int n_slots, int E, int* sorted, int capacity, int* tile_expert, int max_tiles,
@@ -244,6 +503,27 @@ extern "C" int dk_experts_gemm(const void* A, const void* W, void* out, const in
   if (max_tiles == 0) return 0;
   DK_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && top > 0, "experts_gemm: bad sizes tiles=%d N=%d K=%d top=%d", max_tiles, N, K, top);
   DK_REQUIRE(max_tiles <= 65535, "experts_gemm: %d tiles are above the grid's limit", max_tiles);
+  if (dtype == DK_BF16 && K % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0) {
+    const int cols = act ? MMA_BN / 2 : MMA_BN;
+    const dim3 mgrid((N + cols - 1) / cols, max_tiles);
+    static bool granted[DK_MAX_DEVICES] = {false};
+    const int dev = dk_current_device();
+    if (!granted[dev]) {
+      if (cudaFuncSetAttribute(experts_gemm_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM) != cudaSuccess ||
+          cudaFuncSetAttribute(experts_gemm_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM) != cudaSuccess) {
+        cudaGetLastError();
+        DK_REQUIRE(false, "experts_gemm: %d bytes of shared memory were not granted", MMA_SMEM);
+      }
+      granted[dev] = true;
+    }
+    if (act)
+      experts_gemm_mma_kernel<true><<<mgrid, 256, MMA_SMEM, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, out, sorted, tile_expert,
+                                                                      top, N, K, limit, alpha, shift);
+    else
+      experts_gemm_mma_kernel<false><<<mgrid, 256, MMA_SMEM, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, out, sorted, tile_expert,
+                                                                       top, N, K, limit, alpha, shift);
+    return dk_check_launch("experts_gemm");
+  }
   const dim3 grid((N + TILE_N - 1) / TILE_N, max_tiles);
 #define LAUNCH(T)                                                                                                                  \
   do {                                                                                                                             \

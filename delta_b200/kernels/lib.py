@@ -94,9 +94,13 @@ _SIGNATURES = {
     "dk_rows_append_unit": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, I, F, I, I, P, P],
     "dk_decay_attention_slice": [I, I, I, I],
     "dk_decay_attention": [P, I, I, I, I, I, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "dk_decay_attention_chunk": [],
+    "dk_decay_attention_chunked_supported": [I, I],
+    "dk_decay_attention_chunked": [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "dk_gated_rms_norm": [P, P, I, P, P, I, I, F, I, P],
     "dk_glu_clamped": [P, P, L, I, F, F, F, I, P],
     "dk_router_topk": [P, I, P, P, I, I, I, P],
+    "dk_router": [P, P, P, P, P, I, I, I, I, I, I, P],
     "dk_experts_align": [P, I, I, P, I, P, I, P],
     "dk_experts_gemm": [P, P, P, P, P, I, I, I, I, I, F, F, F, I, P],
     "dk_experts_combine": [P, P, I, P, P, I, P, I, I, I, P],

@@ -695,6 +695,33 @@ def decay_attention(src, q_off, k_off, v_off, decays, state, out, *, H, dk, dv, 
     return out
 
 
+def decay_attention_chunk() -> int:
+    """Tokens of a chunk on the path that runs a row's chunks in parallel."""
+    return int(_l.load().dk_decay_attention_chunk())
+
+
+def decay_attention_chunked_supported(dk, dv) -> bool:
+    return bool(_l.load().dk_decay_attention_chunked_supported(int(dk), int(dv)))
+
+
+def decay_attention_chunked(src, q_off, k_off, v_off, decays, state, out, work, chunk_base, max_chunks, *, H, dk, dv, row_slot,
+                            row_q_start, row_q_len, silu=True):
+    """``decay_attention`` for long portions: every row is cut into chunks that run in parallel (three kernels: every chunk's own
+    state, the states before the chunks in order, every chunk's outputs).  ``chunk_base`` [rows] int32: the chunks of all rows
+    before each row; ``work`` float32 with room for (all chunks) x H x dk x dv; ``max_chunks``: the most chunks of a row."""
+    rows = row_slot.shape[0]
+    if tuple(state.shape[1:]) != (H, dk, dv):
+        raise KernelError(f"decay_attention_chunked: the state has shape {tuple(state.shape)}, expected [slots, {H}, {dk}, {dv}]")
+    i32 = torch.int32
+    _l.check(_l.load().dk_decay_attention_chunked(
+        _ptr(src, "src"), src.shape[1], int(q_off), int(k_off), int(v_off), int(bool(silu)), _ptr(decays, "decays", torch.float64),
+        _ptr(state, "state", torch.float32), _ptr(out, "out", torch.float32), _ptr(work, "work", torch.float32),
+        _ptr(row_slot, "row_slot", i32), _ptr(row_q_start, "row_q_start", i32), _ptr(row_q_len, "row_q_len", i32),
+        _ptr(chunk_base, "chunk_base", i32), rows, int(max_chunks), H, dk, dv, dtype_code(src.dtype), _stream()),
+        "decay_attention_chunked", 3)
+    return out
+
+
 def gated_rms_norm(o, gate_ptr, gate_stride, weight, out, eps):
     """out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate) per token; ``o`` float32 [T, n]; the gate's n values of a token
     lie at ``gate_ptr`` + t * ``gate_stride`` elements of the type of ``out``."""
@@ -720,6 +747,15 @@ def router_topk(logits, experts, top, choice, weight):
     T = logits.shape[0]
     _l.check(_l.load().dk_router_topk(_ptr(logits, "logits", torch.float32), logits.shape[1], _ptr(choice, "choice", torch.int32),
                                       _ptr(weight, "weight", torch.float32), T, int(experts), int(top), _stream()), "router_topk")
+
+
+def router(x, w, experts, top, logits, choice, weight):
+    """logits = x w^T in 32 bit ([T, rows of w]; the first ``experts`` rows are the experts'), and per token the ``top`` largest of
+    the experts' logits with the softmax over them."""
+    T, d = x.shape
+    _l.check(_l.load().dk_router(_ptr(x, "x"), _ptr(w, "w", x.dtype), _ptr(logits, "logits", torch.float32), _ptr(choice, "choice", torch.int32),
+                                 _ptr(weight, "weight", torch.float32), T, d, w.shape[0], int(experts), int(top), dtype_code(x.dtype),
+                                 _stream()), "router")
 
 
 def experts_tile_rows() -> int:

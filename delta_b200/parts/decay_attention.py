@@ -6,7 +6,8 @@ With mixer input h, H heads, key size dk and value size dv:
     out = W_o ( rmsnorm(o over all heads) * w * sigmoid(W_g h) )
 A request's state is S [H, dk, dv] in 32 bit, zero at its start, one per run of the layer; a step continues from what
 the request's earlier steps left, so a prompt may be cut anywhere.  The four projections are one product; the
-recurrence, its decays and the norm are 32 bit whatever the compute type.
+recurrence, its decays and the norm are 32 bit whatever the compute type.  Short portions and single tokens run one
+block per (row, head) over the row's chunks in turn; long portions run their chunks in parallel (``csrc/decay_attention.cu``).
 """
 from __future__ import annotations
 
@@ -17,6 +18,7 @@ from . import linear
 from .base import MIXERS, Mixer, StateSpec, TensorSpec
 
 STATE = "decay_attention"
+PARALLEL_FROM = 65      # portions of at least this many tokens run their chunks in parallel
 
 
 @MIXERS.register("decay_attention")
@@ -53,8 +55,22 @@ class DecayAttention(Mixer):
         T = x.shape[0]
         qkvg = linear.linear(ctx, x, self.w_in)                       # [T, 2 H dk + 2 H dv]: q | k | v | g, before activations
         o = torch.empty((T, H * dv), dtype=torch.float32, device=x.device)
-        ops.decay_attention(qkvg, 0, H * dk, 2 * H * dk, self._decays, cache.state[STATE], o, H=H, dk=dk, dv=dv,
-                            row_slot=ctx.row_slot, row_q_start=ctx.row_q_start, row_q_len=ctx.row_q_len, silu=True)
+        rows = dict(row_slot=ctx.row_slot, row_q_start=ctx.row_q_start, row_q_len=ctx.row_q_len)
+        if not ctx.replayable and ctx.max_q_len >= PARALLEL_FROM and ops.decay_attention_chunked_supported(dk, dv):
+            # long portions: the recurrence is linear in the state, so a row's chunks run in parallel and are stitched together
+            chunk = ops.decay_attention_chunk()
+
+            def layout():
+                counts = [-(-n // chunk) for n in ctx.host["q_lens"]]
+                base = [sum(counts[:i]) for i in range(len(counts))]
+                return torch.tensor(base, dtype=torch.int32).to(x.device, non_blocking=True), sum(counts), max(counts)
+            base, total, most = ctx.memo(("decay_attention chunks", chunk), layout)
+            bound = (-(-ctx.max_step_tokens // chunk) + ctx.max_rows) * H * dk * dv
+            work = ctx.scratch("decay_attention.chunks", (total * H * dk * dv,), torch.float32, bound=(bound,))
+            ops.decay_attention_chunked(qkvg, 0, H * dk, 2 * H * dk, self._decays, cache.state[STATE], o, work, base, most, H=H, dk=dk,
+                                        dv=dv, silu=True, **rows)
+        else:
+            ops.decay_attention(qkvg, 0, H * dk, 2 * H * dk, self._decays, cache.state[STATE], o, H=H, dk=dk, dv=dv, silu=True, **rows)
         y = torch.empty((T, H * dv), dtype=x.dtype, device=x.device)
         g_at = qkvg.data_ptr() + (2 * H * dk + H * dv) * qkvg.element_size()
         ops.gated_rms_norm(o, g_at, qkvg.shape[1], self.norm_w, y, self.eps)

@@ -16,7 +16,6 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from . import linear
 from .base import FEED_FORWARDS, FeedForward, TensorSpec
 from .feed_forward import ClampedGLU
 
@@ -62,10 +61,10 @@ class Experts(FeedForward):
     def forward(self, ctx, x):
         T, d, E, top, F = x.shape[0], self.width, self.experts, self.top, self.intermediate
         dev, i32, f32 = x.device, torch.int32, torch.float32
-        z = linear.linear(ctx, x, self.w_router, out_dtype=f32)          # [T, E (+1)]
+        z = torch.empty((T, self.w_router.shape[0]), dtype=f32, device=dev)        # [T, E (+1)]
         choice = torch.empty((T, top), dtype=i32, device=dev)
         weight = torch.empty((T, top), dtype=f32, device=dev)
-        ops.router_topk(z, E, top, choice, weight)
+        ops.router(x, self.w_router, E, top, z, choice, weight)
         tile = ops.experts_tile_rows()
         slots = T * top
         capacity = -(-(slots + (tile - 1) * min(E, slots)) // tile) * tile

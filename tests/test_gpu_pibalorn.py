@@ -147,6 +147,23 @@ def test_long_decoding(tmp_path_factory, which, dtype):
     assert all(g.pool.held_pages == 0 for g in runner.cache.groups.values())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["only_lightning", "mix", "odd"])
+def test_long_portions_run_their_chunks_in_parallel(tmp_path_factory, which, dtype):
+    """Portions long enough for the chunk-parallel recurrence: several chunks, one that ends in the middle of a chunk, rows of
+    unequal length in one batch (some a single token), and a state carried on into single tokens afterwards."""
+    cfg, W, folder = model(tmp_path_factory, which)
+    lengths = [150, 9, 117, 33]
+    toks = [helpers.random_tokens(n, cfg["vocab"], 300 + i) for i, n in enumerate(lengths)]
+    refs = [plain.forward(cfg, W, t)[0] for t in toks]
+    runner = make_runner(folder, which, dtype)
+    steps = [[(0, 0, 100), (1, 0, 8), (2, 0, 17)], [(0, 100, 41), (1, 8, 1), (2, 17, 97), (3, 0, 32)], [(0, 141, 1), (3, 32, 1), (2, 114, 3)]]
+    steps += [[(0, p, 1)] for p in range(142, 150)]
+    res = helpers.run_schedule(runner, toks, steps)
+    noise = rounding_noise(cfg, W, toks, refs) if dtype == "bfloat16" else None
+    print("\nchunks in parallel worst", compare(res, refs, lengths, dtype, "long portions", noise))
+
+
 def test_a_slot_used_again_starts_clean(tmp_path_factory):
     """Request B after request A in the same slot and pages equals B alone: state, previous token and cache of A are gone."""
     from delta_b200.engine.step import RowInput
@@ -206,6 +223,19 @@ def test_decay_attention_kernel(H, dk, dv, dtype):
         t0 += L
     assert torch.equal(state[4].cpu(), state0[4])       # a slot no row names is left alone
     assert worst < 2e-5, worst
+    # the same rows with their chunks in parallel: outputs and end states agree with the path that takes the chunks in turn
+    if ops.decay_attention_chunked_supported(dk, dv):
+        chunk = ops.decay_attention_chunk()
+        counts = [-(-n // chunk) for n in lens]
+        base = torch.tensor([sum(counts[:i]) for i in range(len(lens))], dtype=torch.int32, device=dev)
+        work = torch.empty(sum(counts) * H * dk * dv, dtype=torch.float32, device=dev)
+        state2 = state0.clone().to(dev)
+        out2 = torch.empty_like(out)
+        ops.decay_attention_chunked(src.to(dev), 0, H * dk, 2 * H * dk, torch.tensor(decays, dtype=torch.float64, device=dev), state2, out2,
+                                    work, base, max(counts), H=H, dk=dk, dv=dv, **_rows(lens, slots, dev))
+        scale = out.abs().max().item()
+        assert (out2 - out).abs().max().item() < 2e-5 * scale
+        assert (state2 - state).abs().max().item() < 2e-5 * state.abs().max().item()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -259,6 +289,29 @@ def test_experts_kernels(T, E, top, F, d, dtype):
             ref[t] += torch.sigmoid(z[t, E].double()) * shared[t].double()
         err = (out.cpu().double() - ref).abs().max().item() / ref.abs().max().item()
         assert err < (2e-5 if dtype == torch.float32 else 2e-2), (crowd, err)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,E,top,d,extra", [(1, 4, 2, 40, 1), (19, 7, 7, 50, 0), (70, 33, 5, 333, 1), (9, 3, 1, 2048, 1)])
+def test_router_kernel(T, E, top, d, extra, dtype):
+    """The router's product in 32 bit with its choice: logits, the chosen experts in the order of their logits, the softmax over
+    the chosen ones; a further row of the matrix (a gate's) is computed and left out of the choice."""
+    from delta_b200.kernels import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(T * 7 + E)
+    x = torch.randn(T, d, generator=g).to(dtype)
+    w = (torch.randn(E + extra, d, generator=g) * 3 / d ** 0.5).to(dtype)
+    if extra:
+        w[E] = w[:E].abs().sum(0)          # a row whose logit is far above every expert's
+    z = torch.empty(T, E + extra, dtype=torch.float32, device=dev)
+    choice = torch.empty(T, top, dtype=torch.int32, device=dev)
+    weight = torch.empty(T, top, dtype=torch.float32, device=dev)
+    ops.router(x.to(dev), w.to(dev), E, top, z, choice, weight)
+    ref = x.double() @ w.double().T
+    assert (z.cpu().double() - ref).abs().max().item() < 1e-5 * max(1.0, ref.abs().max().item())
+    vals, idx = torch.topk(z.cpu()[:, :E], top, dim=-1)
+    assert torch.equal(choice.cpu().long(), idx)
+    assert torch.allclose(weight.cpu(), torch.softmax(vals, -1), atol=1e-6)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
