@@ -115,7 +115,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 decay_chunk_state_kernel(const T* __restrict__ src, int src_stride, int k_off, int v_off, int act, const double* __restrict__ decays,
                          float* __restrict__ U, const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
-                         const int* __restrict__ chunk_base, int H, int dk, int dv, int dvs) {
+                         const int* __restrict__ chunk_base, int H, int dk, int dv, int dvs, int vec) {
   extern __shared__ __align__(16) float sm[];
   const int row = blockIdx.y / H, h = blockIdx.y % H, j0 = blockIdx.z * dvs;
   const int jn = min(dvs, dv - j0), c0 = blockIdx.x * PC, n_new = row_q_len[row];
@@ -127,6 +127,32 @@ decay_chunk_state_kernel(const T* __restrict__ src, int src_stride, int k_off, i
   float* pw = V + PC * dvp;          // [PC + 1]
   if (tid <= PC) pw[tid] = (float)pow(decays[h], (double)tid);
   __syncthreads();
+  if (vec) {      // sizes and offsets are multiples of 8: sixteen-byte loads, all of a thread's loads under way at once
+    const int kc = dk / 8, vc = dvp / 8;
+    for (int idx = tid; idx < PC * kc; idx += 256) {
+      const int s = idx / kc, c = (idx - s * kc) * 8;
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (s < n) {
+        load8<T>(src + (size_t)(t0 + s) * src_stride + k_off + (size_t)h * dk + c, v);
+        const float f = pw[n - 1 - s];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = (act ? act_silu(v[e]) : v[e]) * f;
+      }
+      *reinterpret_cast<float4*>(Kd + s * dkp + c) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(Kd + s * dkp + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    for (int idx = tid; idx < PC * vc; idx += 256) {
+      const int s = idx / vc, c = (idx - s * vc) * 8;
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (s < n && c < jn) {
+        load8<T>(src + (size_t)(t0 + s) * src_stride + v_off + (size_t)h * dv + j0 + c, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = act ? act_silu(v[e]) : v[e];
+      }
+      *reinterpret_cast<float4*>(V + s * dvp + c) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(V + s * dvp + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  } else {
   for (int idx = tid; idx < PC * dkp; idx += 256) {
     const int s = idx / dkp, i = idx - s * dkp;
     float v = 0.f;
@@ -146,12 +172,14 @@ decay_chunk_state_kernel(const T* __restrict__ src, int src_stride, int k_off, i
     }
     V[idx] = v;
   }
+  }
   __syncthreads();
   float* Uc = U + ((size_t)(chunk_base[row] + blockIdx.x) * H + h) * dk * dv;
   const int tiles_j = dvp / 4, tiles = (dkp / 4) * tiles_j;
   for (int tile = tid; tile < tiles; tile += 256) {
     const int ti = tile / tiles_j, tj = tile - ti * tiles_j;
     float acc[4][4] = {};
+#pragma unroll 4
     for (int s = 0; s < n; ++s) {
       const float4 a = *reinterpret_cast<const float4*>(Kd + s * dkp + 4 * ti);
       const float4 b = *reinterpret_cast<const float4*>(V + s * dvp + 4 * tj);
@@ -197,7 +225,7 @@ __global__ void __launch_bounds__(128)
 decay_chunk_out_kernel(const T* __restrict__ src, int src_stride, int q_off, int k_off, int v_off, int act,
                        const double* __restrict__ decays, const float* __restrict__ U, float* __restrict__ out,
                        const int* __restrict__ row_q_start, const int* __restrict__ row_q_len, const int* __restrict__ chunk_base,
-                       int H, int dk, int dv, int dvs) {
+                       int H, int dk, int dv, int dvs, int vec) {
   extern __shared__ __align__(16) float sm[];
   const int row = blockIdx.y / H, h = blockIdx.y % H, j0 = blockIdx.z * dvs;
   const int jn = min(dvs, dv - j0), c0 = blockIdx.x * PC, n_new = row_q_len[row];
@@ -211,6 +239,40 @@ decay_chunk_out_kernel(const T* __restrict__ src, int src_stride, int q_off, int
   float* At = V + PC * dvp;          // [PC][PCP]: At[s][t] = lambda^(t-s) q_t . k_s for s <= t, else 0
   float* pw = At + PC * PCP;         // [PC + 1]
   if (tid <= PC) pw[tid] = (float)pow(decays[h], (double)tid);
+  const float* Sc = U + ((size_t)(chunk_base[row] + blockIdx.x) * H + h) * dk * dv;
+  if (vec) {      // sizes and offsets are multiples of 8: sixteen-byte loads, all of a thread's loads under way at once
+    const int kc = dk / 8, vc = dvp / 8, sc = dvp / 4;
+    for (int idx = tid; idx < PC * kc; idx += 128) {      // a warp takes eight entries of all 32 tokens: stores without conflicts
+      const int t = idx % PC, c = (idx / PC) * 8;
+      float q[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, k[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (t < n) {
+        const T* p = src + (size_t)(t0 + t) * src_stride + (size_t)h * dk + c;
+        load8<T>(p + q_off, q);
+        load8<T>(p + k_off, k);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        Qt[(c + e) * PCP + t] = (act && t < n) ? act_silu(q[e]) : q[e];
+        Kt[(c + e) * PCP + t] = (act && t < n) ? act_silu(k[e]) : k[e];
+      }
+    }
+    for (int idx = tid; idx < dk * sc; idx += 128) {
+      const int i = idx / sc, j = (idx - i * sc) * 4;
+      *reinterpret_cast<float4*>(S + i * dvp + j) =
+          j < jn ? *reinterpret_cast<const float4*>(Sc + (size_t)i * dv + j0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int idx = tid; idx < PC * vc; idx += 128) {
+      const int s2 = idx / vc, c = (idx - s2 * vc) * 8;
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (s2 < n && c < jn) {
+        load8<T>(src + (size_t)(t0 + s2) * src_stride + v_off + (size_t)h * dv + j0 + c, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = act ? act_silu(v[e]) : v[e];
+      }
+      *reinterpret_cast<float4*>(V + s2 * dvp + c) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(V + s2 * dvp + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  } else {
   for (int idx = tid; idx < dkp * PC; idx += 128) {
     const int t = idx / dkp, i = idx - t * dkp;
     float qv = 0.f, kv = 0.f;
@@ -226,7 +288,6 @@ decay_chunk_out_kernel(const T* __restrict__ src, int src_stride, int q_off, int
     Qt[i * PCP + t] = qv;
     Kt[i * PCP + t] = kv;
   }
-  const float* Sc = U + ((size_t)(chunk_base[row] + blockIdx.x) * H + h) * dk * dv;
   for (int idx = tid; idx < dkp * dvp; idx += 128) {
     const int i = idx / dvp, j = idx - i * dvp;
     S[idx] = (i < dk && j < jn) ? Sc[(size_t)i * dv + j0 + j] : 0.f;
@@ -240,12 +301,14 @@ decay_chunk_out_kernel(const T* __restrict__ src, int src_stride, int q_off, int
     }
     V[idx] = v;
   }
+  }
   __syncthreads();
   // scores of the chunk: tiles on and below the diagonal
   for (int tile = tid; tile < (PC / 4) * (PC / 4); tile += 128) {
     const int tt = tile / (PC / 4), ts = tile - tt * (PC / 4);
     float acc[4][4] = {};
     if (ts <= tt) {
+#pragma unroll 4
       for (int i = 0; i < dk; ++i) {
         const float4 a = *reinterpret_cast<const float4*>(Qt + i * PCP + 4 * tt);
         const float4 b = *reinterpret_cast<const float4*>(Kt + i * PCP + 4 * ts);
@@ -270,6 +333,7 @@ decay_chunk_out_kernel(const T* __restrict__ src, int src_stride, int q_off, int
     const int tt = tile / tiles_j, tj = tile - tt * tiles_j;
     if (4 * tt >= n) continue;
     float far[4][4] = {}, near[4][4] = {};
+#pragma unroll 4
     for (int i = 0; i < dk; ++i) {
       const float4 a = *reinterpret_cast<const float4*>(Qt + i * PCP + 4 * tt);
       const float4 b = *reinterpret_cast<const float4*>(S + i * dvp + 4 * tj);
@@ -399,6 +463,8 @@ extern "C" int dk_decay_attention_chunked(const void* src, int src_stride, int q
   DK_REQUIRE(sm1 <= SMEM_LIMIT && sm3 <= SMEM_LIMIT, "decay_attention_chunked: heads of %d x %d do not fit the shared memory", dk, dv);
   const dim3 grid(max_chunks, rows * H, (dv + dvs - 1) / dvs);
   const int per_head = dk * dv;
+  const int vec = dk % 8 == 0 && dv % 8 == 0 && dvs % 8 == 0 && src_stride % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
+                  ((uintptr_t)src % 16) == 0 && ((uintptr_t)U % 16) == 0;
   const dim3 scan_grid((per_head + 255) / 256, rows * H);
 #define LAUNCH(T)                                                                                                                       \
   do {                                                                                                                                  \
@@ -408,10 +474,10 @@ extern "C" int dk_decay_attention_chunked(const void* src, int src_stride, int q
       DK_REQUIRE(false, "decay_attention_chunked: shared memory was not granted");                                                      \
     }                                                                                                                                   \
     decay_chunk_state_kernel<T><<<grid, 256, sm1, stream>>>((const T*)src, src_stride, k_off, v_off, act, decays, U, row_q_start,     \
-                                                            row_q_len, chunk_base, H, dk, dv, dvs);                                   \
+                                                            row_q_len, chunk_base, H, dk, dv, dvs, vec);                              \
     decay_chunk_scan_kernel<<<scan_grid, 256, 0, stream>>>(U, state, decays, row_slot, row_q_len, chunk_base, H, per_head);            \
     decay_chunk_out_kernel<T><<<grid, 128, sm3, stream>>>((const T*)src, src_stride, q_off, k_off, v_off, act, decays, U, out,         \
-                                                          row_q_start, row_q_len, chunk_base, H, dk, dv, dvs);                         \
+                                                          row_q_start, row_q_len, chunk_base, H, dk, dv, dvs, vec);                    \
   } while (0)
   if (dtype == DK_F32) LAUNCH(float);
   else if (dtype == DK_BF16) LAUNCH(__nv_bfloat16);
