@@ -413,7 +413,7 @@ def pibalorn_config(d: int) -> dict:
     att = dict(type="attention", mixer=dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, scale=0.09, rot=dict(base=10000.0, dims=64)))
     experts = dict(kind="moe", router=dict(experts=16, top=4), expert=dict(ff=d // 2, limit=7.0), shared=dict(ff=d // 2, limit=7.0))
     return dict(architecture="Pibalorn", vocab=32000, width=d, norm=dict(eps=1e-5),
-                embedding=dict(scale=float(d) ** 0.5, bigram=dict(buckets=4093, mul_prev=127, mul_cur=17)),
+                embedding=dict(scale=float(d) ** 0.5, bigram=dict(buckets=4093, mul_prev=8191, mul_cur=131)),
                 loop=dict(start=1, stop=3, times=2),
                 layers=[dict(lin, mlp=dict(kind="dense", ff=(8 * d // 3 + 255) // 256 * 256, limit=7.0)), dict(att, mlp=experts), dict(lin, mlp=experts),
                         dict(att, mlp=experts)])

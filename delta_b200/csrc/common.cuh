@@ -146,3 +146,13 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, flo
     v[2 * i + 1] = __high2float(h[i]);
   }
 }
+
+// The gated activation with clamped branches:  g' sigmoid(alpha g') (u' + shift),  g' = min(g, limit), u' = clamp(u, -limit, limit)
+// (limit < 0: nothing is clamped).
+__device__ __forceinline__ float dk_glu_value(float g, float u, float limit, float alpha, float shift) {
+  if (limit >= 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  return g * (1.f / (1.f + expf(-alpha * g))) * (u + shift);
+}

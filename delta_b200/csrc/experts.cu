@@ -5,7 +5,7 @@
 //   router          per token the router's logits z = W x in 32 bit, the `top` largest of the E experts' logits (the lowest
 //                   index among equals) and the softmax over the chosen logits only (router_topk: the choice alone, from
 //                   logits that are there already);
-//   experts_align   sorts the (token, choice) slots by expert into tiles of TILE_M rows that each belong to one expert
+//   experts_align   sorts the (token, choice) slots by expert into tiles of `tile_m` rows that each belong to one expert
 //                   (every expert's rows padded to whole tiles with -1), so that the products run as one launch and
 //                   nothing about the routing is read on the host;
 //   experts_gemm    for every tile the product of its rows with its expert's matrix.  First product: rows are gathered
@@ -28,13 +28,7 @@ constexpr int GEMM_THREADS = 256;
 constexpr int MAX_TOP = 32;
 constexpr int MAX_EXPERTS = 1024;
 
-__device__ __forceinline__ float glu_value(float g, float u, float limit, float alpha, float shift) {
-  if (limit >= 0.f) {
-    g = fminf(g, limit);
-    u = fminf(fmaxf(u, -limit), limit);
-  }
-  return g * (1.f / (1.f + expf(-alpha * g))) * (u + shift);
-}
+__device__ __forceinline__ float glu_value(float g, float u, float limit, float alpha, float shift) { return dk_glu_value(g, u, limit, alpha, shift); }
 
 template <typename T>
 __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows, int F, float limit, float alpha, float shift) {
@@ -160,7 +154,7 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restric
 
 // One block.  sorted[p] = slot (token * top + choice) or -1; tile_expert[tile] = expert or -1.
 __global__ void experts_align_kernel(const int* __restrict__ choice, int n_slots, int E, int* __restrict__ sorted, int capacity,
-                                     int* __restrict__ tile_expert, int max_tiles) {
+                                     int* __restrict__ tile_expert, int max_tiles, int tile_m) {
   __shared__ int count[MAX_EXPERTS], start[MAX_EXPERTS];
   for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
   __syncthreads();
@@ -175,9 +169,9 @@ __global__ void experts_align_kernel(const int* __restrict__ choice, int n_slots
     int at = 0;
     for (int e = 0; e < E; ++e) {
       start[e] = at;
-      const int tiles = (count[e] + TILE_M - 1) / TILE_M;
-      for (int q = 0; q < tiles; ++q) tile_expert[at / TILE_M + q] = e;
-      at += tiles * TILE_M;
+      const int tiles = (count[e] + tile_m - 1) / tile_m;
+      for (int q = 0; q < tiles; ++q) tile_expert[at / tile_m + q] = e;
+      at += tiles * tile_m;
       count[e] = 0;
     }
   }
@@ -402,6 +396,17 @@ experts_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
     }
 }
 
+// rows[p] = x[sorted[p] / top] (zeros where sorted[p] < 0): the tokens in the sorted order, for products that want their rows
+// side by side (csrc/gemm_tc.cu).  K is a multiple of 8.
+__global__ void experts_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted, int top,
+                                      __nv_bfloat16* __restrict__ rows, int K) {
+  const int p = blockIdx.x;
+  const int s = sorted[p];
+  const uint4* src = s < 0 ? nullptr : reinterpret_cast<const uint4*>(x + (size_t)(s / top) * K);
+  uint4* dst = reinterpret_cast<uint4*>(rows + (size_t)p * K);
+  for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+}
+
 template <typename T>
 __global__ void experts_combine_kernel(const float* __restrict__ z, const float* __restrict__ weight, int top, const T* __restrict__ shared,
                                        const float* __restrict__ gate_logit, int gate_stride, T* __restrict__ out, int d) {
@@ -471,12 +476,12 @@ extern "C" int dk_router(const void* x, const void* w, float* logits, int* choic
 }
 
 extern "C" int dk_experts_align(const int* choice, int n_slots, int E, int* sorted, int capacity, int* tile_expert, int max_tiles,
-                                cudaStream_t stream) {
+                                int tile_m, cudaStream_t stream) {
   if (n_slots == 0) return 0;
   DK_REQUIRE(n_slots > 0 && E > 0 && E <= MAX_EXPERTS, "experts_align: bad sizes slots=%d E=%d (at most %d experts)", n_slots, E, MAX_EXPERTS);
-  DK_REQUIRE(capacity % TILE_M == 0 && max_tiles * TILE_M == capacity && capacity >= n_slots + (TILE_M - 1) * (E < n_slots ? E : n_slots),
+  DK_REQUIRE(tile_m > 0 && capacity % tile_m == 0 && max_tiles * tile_m == capacity && capacity >= n_slots + (tile_m - 1) * (E < n_slots ? E : n_slots),
              "experts_align: %d rows in %d tiles do not hold %d slots of %d experts", capacity, max_tiles, n_slots, E);
-  experts_align_kernel<<<1, 1024, 0, stream>>>(choice, n_slots, E, sorted, capacity, tile_expert, max_tiles);
+  experts_align_kernel<<<1, 1024, 0, stream>>>(choice, n_slots, E, sorted, capacity, tile_expert, max_tiles, tile_m);
   return dk_check_launch("experts_align");
 }
 
@@ -517,6 +522,14 @@ extern "C" int dk_experts_gemm(const void* A, const void* W, void* out, const in
   else DK_REQUIRE(false, "experts_gemm: unknown dtype %d", dtype);
 #undef LAUNCH
   return dk_check_launch("experts_gemm");
+}
+
+extern "C" int dk_experts_gather(const void* x, const int* sorted, int top, void* rows, int capacity, int K, cudaStream_t stream) {
+  if (capacity == 0) return 0;
+  DK_REQUIRE(capacity > 0 && K > 0 && K % 8 == 0 && top > 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)rows % 16) == 0,
+             "experts_gather: bad arguments capacity=%d K=%d top=%d", capacity, K, top);
+  experts_gather_kernel<<<capacity, K >= 2048 ? 256 : 128, 0, stream>>>((const __nv_bfloat16*)x, sorted, top, (__nv_bfloat16*)rows, K);
+  return dk_check_launch("experts_gather");
 }
 
 extern "C" int dk_experts_combine(const float* z, const float* weight, int top, const void* shared, const float* gate_logit,

@@ -50,6 +50,14 @@ struct TcArgs {
   int tmem_cols;
   int ksub;          // boxes of 64 elements of K per stage (4, or 2 or 1 when many rows leave less room)
   int chunks;        // groups of mpad rows of x: block (tile, chunk) makes rows [chunk * mpad, ...) of the tile's columns
+  // grouped products (a mixture of experts): chunk c of x meets the matrix of expert chunk_expert[c], whose rows start at
+  // expert * expert_rows of W; chunks with a negative expert are left out.  row_map: output row of every row of x (negative:
+  // the row is not stored).  glu: the epilogue is the gated activation with clamped branches instead of silu(gate) * up.
+  const int* chunk_expert;
+  const int* row_map;
+  int expert_rows;
+  int glu;
+  float glu_limit, glu_alpha, glu_shift;
 };
 
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -72,6 +80,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   // a tile of W is fetched from memory once and then found in the L2 by the blocks of the other chunks.
   const int tile = blockIdx.x / a.chunks;
   const int m0 = (blockIdx.x % a.chunks) * a.mpad;    // first row of x and of the output of this block
+  int w_row0 = 0;                                     // first row of this block's matrix in W
+  if (a.chunk_expert != nullptr) {
+    const int expert = a.chunk_expert[blockIdx.x % a.chunks];
+    if (expert < 0) return;                           // before anything is asked for or handed out: the whole block leaves
+    w_row0 = expert * a.expert_rows;
+  }
   const int m_here = min(a.mpad, a.M - m0);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rows_out = a.swiglu ? 64 : TILE_ROWS;    // output columns this tile makes
@@ -101,10 +115,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
       const int kc = ((ks_begin + i) * KSUB + sub) * KSTEP;     // past K the boxes are filled with zeros
       const uint32_t dst = dst0 + sub * a_bytes;
       if (a.swiglu) {
-        tma_load_2d(dst, &map_w, kc, n0, full0 + 8 * s);                           // 64 gate rows
-        tma_load_2d(dst + 64 * KSTEP * 2, &map_w, kc, a.n_up + n0, full0 + 8 * s);  // their 64 up rows
+        tma_load_2d(dst, &map_w, kc, w_row0 + n0, full0 + 8 * s);                           // 64 gate rows
+        tma_load_2d(dst + 64 * KSTEP * 2, &map_w, kc, w_row0 + a.n_up + n0, full0 + 8 * s);  // their 64 up rows
       } else {
-        tma_load_2d(dst, &map_w, kc, n0, full0 + 8 * s);
+        tma_load_2d(dst, &map_w, kc, w_row0 + n0, full0 + 8 * s);
       }
       tma_load_2d(dst0 + KSUB * a_bytes + sub * b_bytes, &map_x, kc, m0, full0 + 8 * s);   // rows past M are zeros
     }
@@ -218,12 +232,20 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     }
     const int n = n0 + r;
     if (good && n < (a.swiglu ? a.n_up : a.N)) {     // N and the first up row are multiples of 8: a group is in or out as a whole
-      if (a.swiglu) {
+      if (a.swiglu && a.glu) {      // both products rounded to bfloat16 first, as separate products would be
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          y[i] = dk_glu_value(__bfloat162float(__float2bfloat16_rn(y[i])), __bfloat162float(__float2bfloat16_rn(u[i])), a.glu_limit,
+                              a.glu_alpha, a.glu_shift);
+      } else if (a.swiglu) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) y[i] = y[i] / (1.f + expf(-y[i])) * u[i];
       }
+      long long out_row = m0 + m;
+      if (a.row_map != nullptr) out_row = a.row_map[m0 + m];
+      if (out_row < 0) continue;
       if (a.out_f32) {
-        float* dst = (float*)a.out + (size_t)(m0 + m) * a.ldc + n;
+        float* dst = (float*)a.out + (size_t)out_row * a.ldc + n;
         *reinterpret_cast<float4*>(dst) = make_float4(y[0], y[1], y[2], y[3]);
         *reinterpret_cast<float4*>(dst + 4) = make_float4(y[4], y[5], y[6], y[7]);
       } else {
@@ -234,7 +256,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         st.y = *reinterpret_cast<uint32_t*>(&p1);
         st.z = *reinterpret_cast<uint32_t*>(&p2);
         st.w = *reinterpret_cast<uint32_t*>(&p3);
-        *reinterpret_cast<uint4*>((__nv_bfloat16*)a.out + (size_t)(m0 + m) * a.ldc + n) = st;
+        *reinterpret_cast<uint4*>((__nv_bfloat16*)a.out + (size_t)out_row * a.ldc + n) = st;
       }
     }
   }
@@ -284,6 +306,11 @@ extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N,
   DK_REQUIRE((ldc % 8) == 0 && ((uintptr_t)out % 16) == 0,
              "gemm_tc: the output must start on a 16-byte boundary with a leading size that is a multiple of 8");
   TcArgs a;
+  a.chunk_expert = nullptr;
+  a.row_map = nullptr;
+  a.expert_rows = 0;
+  a.glu = 0;
+  a.glu_limit = a.glu_alpha = a.glu_shift = 0.f;
   a.out = out;
   a.err = err;
   a.M = M; a.N = N; a.K = K; a.ldc = ldc;
@@ -340,4 +367,86 @@ extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N,
     return DK_ERR_LAUNCH;
   }
   return dk_check_launch("gemm_tc");
+}
+
+// Grouped products for a mixture of experts: x [M, K] holds the rows of all experts in tiles of `tile_m` (128 or 256) rows,
+// tile c belonging to expert chunk_expert[c] (negative: no rows); W [E * expert_rows, K] holds the experts' matrices one
+// after the other, [gate (n) | up (n)] rows each when `glu`, else n rows.  out[row_map ? row_map[r] : r][0..n) for every row
+// r of x (rows mapped to a negative number are not stored).  One block per (128 rows of an expert's matrix, tile of x).
+extern "C" int dk_experts_gemm_tc_supported(int n, int K, int glu) {
+  return dk_gemm_tc_supported(128, glu ? 2 * n : n, K, glu);
+}
+
+extern "C" int dk_experts_gemm_tc(const void* x, const void* W, void* out, const int* chunk_expert, const int* row_map, int M,
+                                  int tile_m, int n, int K, int E, int ldc, int out_dtype, int glu, float limit, float alpha,
+                                  float shift, int* err, cudaStream_t stream) {
+  if (M == 0) return 0;
+  DK_REQUIRE(tile_m == 128 || tile_m == 256, "experts_gemm_tc: tiles of 128 or 256 rows, got %d", tile_m);
+  DK_REQUIRE(M > 0 && M % tile_m == 0 && E > 0, "experts_gemm_tc: %d rows are no whole tiles of %d", M, tile_m);
+  DK_REQUIRE(dk_experts_gemm_tc_supported(n, K, glu), "experts_gemm_tc: sizes not taken: n=%d K=%d glu=%d", n, K, glu);
+  DK_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)out % 16) == 0 && (ldc % 8) == 0,
+             "experts_gemm_tc: operands must start on 16-byte boundaries with leading sizes that are multiples of 8");
+  DK_REQUIRE(out_dtype == DK_BF16 || out_dtype == DK_F32, "experts_gemm_tc: unknown output dtype %d", out_dtype);
+  DK_REQUIRE(chunk_expert != nullptr, "experts_gemm_tc: no tile map");
+  TcArgs a;
+  a.chunk_expert = chunk_expert;
+  a.row_map = row_map;
+  a.expert_rows = glu ? 2 * n : n;
+  a.glu = glu;
+  a.glu_limit = limit; a.glu_alpha = alpha; a.glu_shift = shift;
+  a.out = out;
+  a.err = err;
+  a.M = M; a.N = n; a.K = K; a.ldc = ldc;
+  a.mpad = tile_m;
+  a.chunks = M / tile_m;
+  a.out_f32 = out_dtype == DK_F32;
+  a.swiglu = glu;
+  a.n_up = glu ? n : 0;
+  a.tmem_cols = tile_m;
+  const int a_bytes = TILE_ROWS * KSTEP * 2;
+  const int b_bytes = a.mpad * KSTEP * 2;
+  a.ksub = a.mpad <= 128 ? 2 : 1;
+  const int stage_bytes = a.ksub * (a_bytes + b_bytes);
+  const int part_bytes = a.mpad * TILE_ROWS * 4;
+  int stages = (224 * 1024 - 2048) / stage_bytes;
+  if (stages > 8) stages = 8;
+  DK_REQUIRE(stages >= 2, "experts_gemm_tc: no room for two stages");
+  a.stages = stages;
+  size_t smem = (size_t)stages * stage_bytes;
+  if (smem < (size_t)part_bytes) smem = part_bytes;
+  smem += 1024;
+  CUtensorMap map_w, map_x;
+  DK_REQUIRE(make_map(&map_w, W, (long long)E * a.expert_rows, K, K, glu ? 64 : TILE_ROWS), "experts_gemm_tc: cannot encode the tensor map of W");
+  DK_REQUIRE(make_map(&map_x, x, M, K, K, a.mpad), "experts_gemm_tc: cannot encode the tensor map of x");
+  static size_t configured_on[DK_MAX_DEVICES] = {0};
+  size_t& configured = configured_on[dk_current_device()];
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      dk_set_error("experts_gemm_tc: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      return DK_ERR_LAUNCH;
+    }
+    configured = smem;
+  }
+  const int rows_out = glu ? 64 : TILE_ROWS;
+  const int tiles = (n + rows_out - 1) / rows_out;
+  cudaLaunchConfig_t cfg = {};
+  DK_REQUIRE((long long)tiles * a.chunks < (1ll << 31), "experts_gemm_tc: too many blocks");
+  cfg.gridDim = dim3(tiles * a.chunks, 1, 1);
+  cfg.blockDim = dim3(TC_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel, map_w, map_x, a);
+  if (e != cudaSuccess) {
+    dk_set_error("experts_gemm_tc: launch failed: %s", cudaGetErrorString(e));
+    return DK_ERR_LAUNCH;
+  }
+  return dk_check_launch("experts_gemm_tc");
 }

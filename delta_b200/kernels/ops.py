@@ -762,10 +762,38 @@ def experts_tile_rows() -> int:
     return int(_l.load().dk_experts_tile_rows())
 
 
-def experts_align(choice, experts, sorted_slots, tile_expert):
+def experts_align(choice, experts, sorted_slots, tile_expert, tile_rows=None):
+    """Sorts the (token, choice) slots by expert into tiles of ``tile_rows`` rows of one expert each: ``sorted_slots`` [tiles *
+    tile_rows] holds slot numbers (token * top + choice) or -1, ``tile_expert`` [tiles] the expert of every tile or -1."""
+    tile_rows = tile_rows or experts_tile_rows()
     _l.check(_l.load().dk_experts_align(_ptr(choice, "choice", torch.int32), choice.numel(), int(experts),
                                         _ptr(sorted_slots, "sorted_slots", torch.int32), sorted_slots.numel(),
-                                        _ptr(tile_expert, "tile_expert", torch.int32), tile_expert.numel(), _stream()), "experts_align")
+                                        _ptr(tile_expert, "tile_expert", torch.int32), tile_expert.numel(), int(tile_rows), _stream()),
+             "experts_align")
+
+
+def experts_gather(x, sorted_slots, top, rows):
+    """rows[p] = x[sorted_slots[p] // top] (zeros where the slot is -1); bfloat16, the width a multiple of 8."""
+    _l.check(_l.load().dk_experts_gather(_ptr(x, "x", torch.bfloat16), _ptr(sorted_slots, "sorted_slots", torch.int32), int(top),
+                                         _ptr(rows, "rows", torch.bfloat16), rows.shape[0], x.shape[1], _stream()), "experts_gather")
+    return rows
+
+
+def experts_gemm_tc_supported(n, k, glu=False) -> bool:
+    return bool(_l.load().dk_experts_gemm_tc_supported(int(n), int(k), int(bool(glu))))
+
+
+def experts_gemm_tc(rows, w, out, tile_expert, tile_rows, *, n, row_map=None, glu=False, limit=-1.0, alpha=1.702, shift=1.0, err=None):
+    """The experts' products on the tcgen05 tensor cores: ``rows`` [tiles * tile_rows, k] (bfloat16, tiles of 128 or 256 rows of
+    one expert each), ``w`` [E, n (2n with ``glu``: gate rows, then up rows), k]; ``out`` row r (or ``row_map[r]``; negative: not
+    stored) takes the n results of row r, after the gated activation when ``glu``."""
+    E, k = w.shape[0], w.shape[2]
+    _l.check(_l.load().dk_experts_gemm_tc(_ptr(rows, "rows", torch.bfloat16), _ptr(w, "w", torch.bfloat16), _ptr(out, "out"),
+                                          _ptr(tile_expert, "tile_expert", torch.int32), _ptr(row_map, "row_map", torch.int32),
+                                          rows.shape[0], int(tile_rows), int(n), int(k), int(E), out.stride(0), dtype_code(out.dtype),
+                                          int(bool(glu)), float(limit), float(alpha), float(shift), _ptr(err, "err", torch.int32),
+                                          _stream()), "experts_gemm_tc")
+    return out
 
 
 def experts_gemm(a, w, out, sorted_slots, tile_expert, *, top, n, k, act=False, limit=-1.0, alpha=1.702, shift=1.0):

@@ -6,7 +6,9 @@
     out = sum over the chosen experts of weight * expert(h)  (+ sigmoid(w_sg . h) * shared(h) when there is a shared expert,
           a feed-forward of the same form that every token runs)
 Nothing about the routing is read on the host: the (token, choice) pairs are sorted by expert on the device into tiles of
-rows of one expert, and the two products of all experts are one launch each (``csrc/experts.cu``).  The router's rows and
+rows of one expert, and the two products of all experts are one launch each: warp-level MMA over tiles of 64 rows
+(``csrc/experts.cu``), or, when a step brings many rows an expert, the tcgen05 product over tiles of 128 rows gathered side
+by side (``csrc/gemm_tc.cu``).  The router's rows and
 the shared expert's gate row are one matrix, so one product gives both.
 """
 from __future__ import annotations
@@ -18,6 +20,10 @@ import torch
 from ..kernels import ops
 from .base import FEED_FORWARDS, FeedForward, TensorSpec
 from .feed_forward import ClampedGLU
+
+
+TC_TILE = 128               # rows of a tile on the tcgen05 path
+TC_ROWS_PER_EXPERT = 96     # from this many rows an expert on average, the products go to the tcgen05 kernel
 
 
 @FEED_FORWARDS.register("experts")
@@ -65,17 +71,26 @@ class Experts(FeedForward):
         choice = torch.empty((T, top), dtype=i32, device=dev)
         weight = torch.empty((T, top), dtype=f32, device=dev)
         ops.router(x, self.w_router, E, top, z, choice, weight)
-        tile = ops.experts_tile_rows()
         slots = T * top
+        # many rows an expert (prompt portions): tiles of 128 rows through the tcgen05 product; else tiles of 64 through warp-level MMA
+        many = (x.dtype == torch.bfloat16 and "products" not in ctx.plain_kernels and slots >= TC_ROWS_PER_EXPERT * E and
+                ops.experts_gemm_tc_supported(F, d, True) and ops.experts_gemm_tc_supported(d, F, False))
+        tile = TC_TILE if many else ops.experts_tile_rows()
         capacity = -(-(slots + (tile - 1) * min(E, slots)) // tile) * tile
         sorted_slots = torch.empty(capacity, dtype=i32, device=dev)
         tile_expert = torch.empty(capacity // tile, dtype=i32, device=dev)
-        ops.experts_align(choice, E, sorted_slots, tile_expert)
+        ops.experts_align(choice, E, sorted_slots, tile_expert, tile)
         y = torch.empty((capacity, F), dtype=x.dtype, device=dev)
-        ops.experts_gemm(x, self.w1, y, sorted_slots, tile_expert, top=top, n=F, k=d, act=True, limit=self.limit, alpha=self.alpha,
-                         shift=self.shift)
         out_slots = torch.empty((slots, d), dtype=f32, device=dev)
-        ops.experts_gemm(y, self.w2, out_slots, sorted_slots, tile_expert, top=top, n=d, k=F)
+        if many:
+            rows = ops.experts_gather(x, sorted_slots, top, torch.empty((capacity, d), dtype=x.dtype, device=dev))
+            ops.experts_gemm_tc(rows, self.w1, y, tile_expert, tile, n=F, glu=True, limit=self.limit, alpha=self.alpha, shift=self.shift,
+                                err=ctx.err)
+            ops.experts_gemm_tc(y, self.w2, out_slots, tile_expert, tile, n=d, row_map=sorted_slots, err=ctx.err)
+        else:
+            ops.experts_gemm(x, self.w1, y, sorted_slots, tile_expert, top=top, n=F, k=d, act=True, limit=self.limit, alpha=self.alpha,
+                             shift=self.shift)
+            ops.experts_gemm(y, self.w2, out_slots, sorted_slots, tile_expert, top=top, n=d, k=F)
         out = torch.empty((T, d), dtype=x.dtype, device=dev)
         if self.shared is not None:
             s = self.shared.forward(ctx, x)

@@ -59,6 +59,10 @@ def config(which: str) -> dict:
     if which == "sharp":    # a large scale on unit-normed heads: single far keys carry most of the weight; tiny pages
         return dict(base, vocab=97, width=64, embedding=dict(scale=2.0), layers=[
             bare(attention(4, 2, 16, 1.5, rot_dims=8, base=100.0)), bare(attention(2, 1, 32, 1.0, rot_dims=32, base=20000.0))])
+    if which == "wide":     # sizes that the tensor-core kernels take (multiples of 64): long portions send the experts' products to the
+        return dict(base, vocab=200, width=128, embedding=dict(scale=2.0), layers=[      # tcgen05 kernel, short ones to warp-level MMA
+            moe(lightning(2, 64, 64, (0.98, 0.8)), 4, 2, 64, 1.1, shared=(64, 1.3)),
+            moe(attention(4, 2, 32, 0.3, rot_dims=16, base=5000.0), 3, 1, 128, 0.9)])
     if which == "only_attention":
         return dict(base, vocab=97, width=40, layers=[bare(attention(4, 2, 16, 0.4, rot_dims=12, base=500.0))])
     if which == "only_lightning":
@@ -75,7 +79,7 @@ def config(which: str) -> dict:
     raise KeyError(which)
 
 
-PAGE_SIZE = {"mix": 16, "odd": 2, "one": 4, "sharp": 4, "only_attention": 8, "only_lightning": 16, "only_experts": 16, "only_pairs": 8,
+PAGE_SIZE = {"wide": 16, "mix": 16, "odd": 2, "one": 4, "sharp": 4, "only_attention": 8, "only_lightning": 16, "only_experts": 16, "only_pairs": 8,
              "pairs_many": 16}
 
 

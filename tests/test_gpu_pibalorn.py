@@ -22,7 +22,7 @@ ROOT = Path(__file__).resolve().parent.parent
 # reference.  bfloat16: the root mean square of a position's differences as a fraction of that of the request's
 # reference logits, and at most three times what rounding alone causes.
 TOL = {"float32": 2e-5, "bfloat16": 6e-2}
-LENGTHS = {"mix": [3, 37, 60, 121], "odd": [1, 7, 26, 45], "one": [2, 25, 33, 58], "sharp": [1, 40, 97, 150], "only_attention": [2, 30, 47],
+LENGTHS = {"wide": [250, 5, 199, 64], "mix": [3, 37, 60, 121], "odd": [1, 7, 26, 45], "one": [2, 25, 33, 58], "sharp": [1, 40, 97, 150], "only_attention": [2, 30, 47],
            "only_lightning": [1, 9, 40, 75], "only_experts": [1, 6, 21, 50], "only_pairs": [1, 2, 19], "pairs_many": [2, 33]}
 _cache = {}
 
@@ -289,6 +289,46 @@ def test_experts_kernels(T, E, top, F, d, dtype):
             ref[t] += torch.sigmoid(z[t, E].double()) * shared[t].double()
         err = (out.cpu().double() - ref).abs().max().item() / ref.abs().max().item()
         assert err < (2e-5 if dtype == torch.float32 else 2e-2), (crowd, err)
+
+
+@pytest.mark.parametrize("T,E,top,F,d", [(700, 4, 2, 64, 128), (300, 3, 3, 128, 72), (1030, 5, 1, 192, 256)])
+def test_experts_products_on_tcgen05(T, E, top, F, d):
+    """The experts' products through the tcgen05 kernel (tiles of 128 rows gathered side by side) against the warp-level MMA
+    path on the same routing: an expert with no rows at all, one with more than two tiles, and a tile that is nearly empty."""
+    from delta_b200.kernels import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(T + F)
+    bf = torch.bfloat16
+    x = torch.randn(T, d, generator=g).to(bf).to(dev)
+    w1 = (torch.randn(E, 2 * F, d, generator=g) / d ** 0.5).to(bf).to(dev)
+    w2 = (torch.randn(E, d, F, generator=g) / F ** 0.5).to(bf).to(dev)
+    z = torch.randn(T, E, generator=g)
+    if E > top:
+        z[:, 1] -= 100.0             # nobody chooses expert 1
+    choice = torch.empty(T, top, dtype=torch.int32, device=dev)
+    weight = torch.empty(T, top, dtype=torch.float32, device=dev)
+    ops.router_topk(z.to(dev), E, top, choice, weight)
+    assert ops.experts_gemm_tc_supported(F, d, True) and ops.experts_gemm_tc_supported(d, F, False)
+    outs = []
+    err = ops.new_error_record(dev)
+    for tile in (ops.experts_tile_rows(), 128):
+        cap = -(-(T * top + (tile - 1) * min(E, T * top)) // tile) * tile
+        ss = torch.empty(cap, dtype=torch.int32, device=dev)
+        te = torch.empty(cap // tile, dtype=torch.int32, device=dev)
+        ops.experts_align(choice, E, ss, te, tile)
+        y = torch.zeros(cap, F, dtype=bf, device=dev)
+        zs = torch.full((T * top, d), float("nan"), dtype=torch.float32, device=dev)
+        if tile == 128:
+            rows = ops.experts_gather(x, ss, top, torch.empty(cap, d, dtype=bf, device=dev))
+            ops.experts_gemm_tc(rows, w1, y, te, tile, n=F, glu=True, limit=0.9, err=err)
+            ops.experts_gemm_tc(y, w2, zs, te, tile, n=d, row_map=ss, err=err)
+            ops.raise_if_error(err)
+        else:
+            ops.experts_gemm(x, w1, y, ss, te, top=top, n=F, k=d, act=True, limit=0.9)
+            ops.experts_gemm(y, w2, zs, ss, te, top=top, n=d, k=F)
+        outs.append(zs.cpu())
+    assert torch.isfinite(outs[1]).all()
+    assert (outs[0] - outs[1]).abs().max().item() <= 2e-2 * outs[0].abs().max().item()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

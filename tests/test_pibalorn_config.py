@@ -8,7 +8,7 @@ import torch
 import pibalorn_helpers as ph
 import plain_pibalorn as plain
 
-ALL = ["mix", "odd", "one", "sharp", "only_attention", "only_lightning", "only_experts", "only_pairs", "pairs_many"]
+ALL = ["wide", "mix", "odd", "one", "sharp", "only_attention", "only_lightning", "only_experts", "only_pairs", "pairs_many"]
 
 
 def build(which):
