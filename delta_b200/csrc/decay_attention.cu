@@ -99,6 +99,69 @@ decay_attention_kernel(const T* __restrict__ src, int src_stride, int q_off, int
   }
 }
 
+// ---- single tokens (decode steps): the state streams through registers once ---------------------------------------------
+// One block per (row, head, 128 value entries): 8 groups of 32 lanes; a lane owns four neighbouring value entries (16-byte
+// accesses, a state row is read by consecutive lanes), group g the key entries g, g + 8, ...  Every thread has all its loads
+// under way at once; S <- lambda S + k v^T is written back in place and o = S^T q is summed over the groups in shared memory.
+// The value size is a multiple of 4.
+template <typename T>
+__global__ void __launch_bounds__(256)
+decay_step_kernel(const T* __restrict__ src, int src_stride, int q_off, int k_off, int v_off, int act, const double* __restrict__ decays,
+                  float* __restrict__ state, float* __restrict__ out, const int* __restrict__ row_slot,
+                  const int* __restrict__ row_q_start, int H, int dk, int dv) {
+  extern __shared__ __align__(16) float sm[];
+  float* q = sm;                       // [dk]
+  float* k = q + dk;                   // [dk]
+  float4* red = reinterpret_cast<float4*>(k + dk + ((2 * dk) & 2));   // [8][32], on the next 16-byte boundary
+  const int row = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, grp = tid >> 5;
+  const int t = row_q_start[row];
+  const T* tok = src + (size_t)t * src_stride;
+  for (int i = tid; i < dk; i += 256) {
+    const float qv = to_f32<T>(tok[q_off + (size_t)h * dk + i]), kv = to_f32<T>(tok[k_off + (size_t)h * dk + i]);
+    q[i] = act ? act_silu(qv) : qv;
+    k[i] = act ? act_silu(kv) : kv;
+  }
+  const int j = blockIdx.z * 128 + lane * 4;
+  const bool live = j < dv;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    const T* vp = tok + v_off + (size_t)h * dv + j;
+    v = make_float4(to_f32<T>(vp[0]), to_f32<T>(vp[1]), to_f32<T>(vp[2]), to_f32<T>(vp[3]));
+    if (act) v = make_float4(act_silu(v.x), act_silu(v.y), act_silu(v.z), act_silu(v.w));
+  }
+  const float lam = (float)decays[h];
+  __syncthreads();
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    float* st = state + (((size_t)row_slot[row] * H + h) * dk) * dv + j;
+#pragma unroll 4
+    for (int i = grp; i < dk; i += 8) {
+      float4 s4 = *reinterpret_cast<const float4*>(st + (size_t)i * dv);
+      const float ki = k[i], qi = q[i];
+      s4.x = fmaf(lam, s4.x, ki * v.x);
+      s4.y = fmaf(lam, s4.y, ki * v.y);
+      s4.z = fmaf(lam, s4.z, ki * v.z);
+      s4.w = fmaf(lam, s4.w, ki * v.w);
+      *reinterpret_cast<float4*>(st + (size_t)i * dv) = s4;
+      o.x = fmaf(qi, s4.x, o.x);
+      o.y = fmaf(qi, s4.y, o.y);
+      o.z = fmaf(qi, s4.z, o.z);
+      o.w = fmaf(qi, s4.w, o.w);
+    }
+  }
+  red[grp * 32 + lane] = o;
+  __syncthreads();
+  if (grp == 0 && live) {
+    float4 a = red[lane];
+#pragma unroll
+    for (int g = 1; g < 8; ++g) {
+      const float4 b = red[g * 32 + lane];
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    *reinterpret_cast<float4*>(out + (size_t)t * ((size_t)H * dv) + (size_t)h * dv + j) = a;
+  }
+}
+
 // ---- long portions: the chunks of a row run in parallel --------------------------------------------------------------
 // The recurrence is linear in the state, so with U_c = sum_s lambda^(n-1-s) k_s v_s^T of chunk c taken alone:
 //   1. decay_chunk_state: U_c for every chunk of every row, in parallel;
@@ -484,4 +547,27 @@ extern "C" int dk_decay_attention_chunked(const void* src, int src_stride, int q
   else DK_REQUIRE(false, "decay_attention_chunked: unknown dtype %d", dtype);
 #undef LAUNCH
   return dk_check_launch("decay_attention_chunked");
+}
+
+// Decode steps: every row brings one token.  The value size is a multiple of 4 and state and output are 16-byte aligned.
+extern "C" int dk_decay_attention_step_supported(int dk, int dv) { return dv % 4 == 0 && (size_t)(2 * dk + 4) * 4 + 8 * 32 * 16 <= 48 * 1024; }
+
+extern "C" int dk_decay_attention_step(const void* src, int src_stride, int q_off, int k_off, int v_off, int act, const double* decays,
+                                       float* state, float* out, const int* row_slot, const int* row_q_start, int rows, int H, int dk,
+                                       int dv, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  DK_REQUIRE(rows > 0 && H > 0 && dk > 0 && dv > 0, "decay_attention_step: bad sizes rows=%d H=%d dk=%d dv=%d", rows, H, dk, dv);
+  DK_REQUIRE(dk_decay_attention_step_supported(dk, dv) && ((uintptr_t)state % 16) == 0 && ((uintptr_t)out % 16) == 0,
+             "decay_attention_step: heads of %d x %d are not taken (the value size must be a multiple of 4)", dk, dv);
+  DK_REQUIRE(H <= 65535, "decay_attention_step: %d heads are above the grid's limit", H);
+  const dim3 grid(rows, H, (dv + 127) / 128);
+  const size_t smem = (size_t)(2 * dk + 4) * sizeof(float) + 8 * 32 * sizeof(float4);
+  if (dtype == DK_F32)
+    decay_step_kernel<float><<<grid, 256, smem, stream>>>((const float*)src, src_stride, q_off, k_off, v_off, act, decays, state, out, row_slot,
+                                                          row_q_start, H, dk, dv);
+  else if (dtype == DK_BF16)
+    decay_step_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)src, src_stride, q_off, k_off, v_off, act, decays, state,
+                                                                  out, row_slot, row_q_start, H, dk, dv);
+  else DK_REQUIRE(false, "decay_attention_step: unknown dtype %d", dtype);
+  return dk_check_launch("decay_attention_step");
 }

@@ -97,6 +97,8 @@ _SIGNATURES = {
     "dk_decay_attention_chunk": [],
     "dk_decay_attention_chunked_supported": [I, I],
     "dk_decay_attention_chunked": [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "dk_decay_attention_step_supported": [I, I],
+    "dk_decay_attention_step": [P, I, I, I, I, I, P, P, P, P, P, I, I, I, I, I, P],
     "dk_gated_rms_norm": [P, P, I, P, P, I, I, F, I, P],
     "dk_glu_clamped": [P, P, L, I, F, F, F, I, P],
     "dk_router_topk": [P, I, P, P, I, I, I, P],

@@ -695,6 +695,22 @@ def decay_attention(src, q_off, k_off, v_off, decays, state, out, *, H, dk, dv, 
     return out
 
 
+def decay_attention_step_supported(dk, dv) -> bool:
+    return bool(_l.load().dk_decay_attention_step_supported(int(dk), int(dv)))
+
+
+def decay_attention_step(src, q_off, k_off, v_off, decays, state, out, *, H, dk, dv, row_slot, row_q_start, silu=True):
+    """``decay_attention`` for steps in which every row brings one token: the state streams through registers once."""
+    if tuple(state.shape[1:]) != (H, dk, dv):
+        raise KernelError(f"decay_attention_step: the state has shape {tuple(state.shape)}, expected [slots, {H}, {dk}, {dv}]")
+    i32 = torch.int32
+    _l.check(_l.load().dk_decay_attention_step(
+        _ptr(src, "src"), src.shape[1], int(q_off), int(k_off), int(v_off), int(bool(silu)), _ptr(decays, "decays", torch.float64),
+        _ptr(state, "state", torch.float32), _ptr(out, "out", torch.float32), _ptr(row_slot, "row_slot", i32),
+        _ptr(row_q_start, "row_q_start", i32), row_slot.shape[0], H, dk, dv, dtype_code(src.dtype), _stream()), "decay_attention_step")
+    return out
+
+
 def decay_attention_chunk() -> int:
     """Tokens of a chunk on the path that runs a row's chunks in parallel."""
     return int(_l.load().dk_decay_attention_chunk())

@@ -6,8 +6,8 @@ With mixer input h, H heads, key size dk and value size dv:
     out = W_o ( rmsnorm(o over all heads) * w * sigmoid(W_g h) )
 A request's state is S [H, dk, dv] in 32 bit, zero at its start, one per run of the layer; a step continues from what
 the request's earlier steps left, so a prompt may be cut anywhere.  The four projections are one product; the
-recurrence, its decays and the norm are 32 bit whatever the compute type.  Short portions and single tokens run one
-block per (row, head) over the row's chunks in turn; long portions run their chunks in parallel (``csrc/decay_attention.cu``).
+recurrence, its decays and the norm are 32 bit whatever the compute type.  Steps of single tokens stream the state through
+registers once; short portions run one block per (row, head) over the row's chunks in turn; long portions run their chunks in parallel (``csrc/decay_attention.cu``).
 """
 from __future__ import annotations
 
@@ -69,6 +69,9 @@ class DecayAttention(Mixer):
             work = ctx.scratch("decay_attention.chunks", (total * H * dk * dv,), torch.float32, bound=(bound,))
             ops.decay_attention_chunked(qkvg, 0, H * dk, 2 * H * dk, self._decays, cache.state[STATE], o, work, base, most, H=H, dk=dk,
                                         dv=dv, silu=True, **rows)
+        elif ctx.decode_only and ops.decay_attention_step_supported(dk, dv):
+            ops.decay_attention_step(qkvg, 0, H * dk, 2 * H * dk, self._decays, cache.state[STATE], o, H=H, dk=dk, dv=dv, silu=True,
+                                     row_slot=ctx.row_slot, row_q_start=ctx.row_q_start)
         else:
             ops.decay_attention(qkvg, 0, H * dk, 2 * H * dk, self._decays, cache.state[STATE], o, H=H, dk=dk, dv=dv, silu=True, **rows)
         y = torch.empty((T, H * dv), dtype=x.dtype, device=x.device)

@@ -407,6 +407,37 @@ def test_rows_append_unit_kernel(dtype):
     assert torch.equal(sd.cpu()[:, H * dk:], src[:, H * dk:])      # keys are not changed in place
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,dk,dv", [(2, 16, 8), (3, 6, 12), (1, 128, 128), (2, 50, 200)])
+def test_decay_attention_step_kernel(H, dk, dv, dtype):
+    """Steps of single tokens: the kernel that streams the state once agrees with the chunked one, outputs and states, for rows
+    in slots out of order and from states that are not zero."""
+    from delta_b200.kernels import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(dk + dv)
+    slots = [3, 0, 2]
+    rows = len(slots)
+    src = (torch.randn(rows, 2 * H * dk + H * dv + 3, generator=g) * 0.8).to(dtype).to(dev)
+    decays = torch.tensor([0.999, 0.3, 0.9][:H], dtype=torch.float64, device=dev)
+    state0 = torch.randn(5, H, dk, dv, generator=g) * 0.5
+    assert ops.decay_attention_step_supported(dk, dv)
+    outs, states = [], []
+    for step in (False, True):
+        state = state0.clone().to(dev)
+        out = torch.empty(rows, H * dv, dtype=torch.float32, device=dev)
+        kw = dict(H=H, dk=dk, dv=dv)
+        r = _rows([1] * rows, slots, dev)
+        if step:
+            ops.decay_attention_step(src, 0, H * dk, 2 * H * dk, decays, state, out, row_slot=r["row_slot"], row_q_start=r["row_q_start"], **kw)
+        else:
+            ops.decay_attention(src, 0, H * dk, 2 * H * dk, decays, state, out, **r, **kw)
+        outs.append(out.cpu())
+        states.append(state.cpu())
+    assert (outs[0] - outs[1]).abs().max().item() <= 1e-5 * outs[0].abs().max().item()
+    assert (states[0] - states[1]).abs().max().item() <= 1e-5 * states[0].abs().max().item()
+    assert torch.equal(states[1][1], state0[1]) and torch.equal(states[1][4], state0[4])
+
+
 # ---- through the engine's own entry points -----------------------------------------------------------------------
 
 def greedy_plain(cfg, W, prompt, n_new):
