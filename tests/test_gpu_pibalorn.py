@@ -355,6 +355,23 @@ def test_router_kernel(T, E, top, d, extra, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("F", [24, 9, 256])
+@pytest.mark.parametrize("limit", [-1.0, 0.0, 1.2])
+def test_glu_clamped_kernel(F, limit, dtype):
+    """Both forms of the kernel (eight entries a thread, one entry a thread); no limit, a limit of zero taken literally, a limit."""
+    from delta_b200.kernels import ops
+    g = torch.Generator().manual_seed(F)
+    gu = (torch.randn(13, 2 * F, generator=g) * 2).to(dtype)
+    out = torch.empty(13, F, dtype=dtype, device="cuda:0")
+    ops.glu_clamped(gu.to("cuda:0"), out, limit)
+    a, b = gu[:, :F].double(), gu[:, F:].double()
+    if limit >= 0:
+        a, b = a.clamp(max=limit), b.clamp(-limit, limit)
+    ref = a * torch.sigmoid(1.702 * a) * (b + 1)
+    assert (out.cpu().double() - ref).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("kind", ["layer", "rms"])
 def test_residual_norm_kernel(kind, dtype):
     from delta_b200.kernels import ops
