@@ -266,6 +266,21 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   }
 }
 
+// The kernel's allowance of dynamic shared memory only ever grows, and both launchers below keep one record of it per
+// device: a second record would let one launcher lower what the other believes it has.
+bool grant_shared_memory(size_t smem) {
+  static size_t configured_on[DK_MAX_DEVICES] = {0};
+  size_t& configured = configured_on[dk_current_device()];
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    configured = smem;
+  }
+  return true;
+}
+
 bool make_map(CUtensorMap* m, const void* base, int rows, int K, int ld, int box_rows) {
   return make_tensor_map_bf16(m, base, rows, K, ld, box_rows);
 }
@@ -335,15 +350,9 @@ extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N,
   CUtensorMap map_w, map_x;
   DK_REQUIRE(make_map(&map_w, W, N, K, ldw, swiglu ? 64 : TILE_ROWS), "gemm_tc: cannot encode the tensor map of W");
   DK_REQUIRE(make_map(&map_x, x, M, K, lda, a.mpad), "gemm_tc: cannot encode the tensor map of x");
-  static size_t configured_on[DK_MAX_DEVICES] = {0};
-  size_t& configured = configured_on[dk_current_device()];
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) {
-      dk_set_error("gemm_tc: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-      return DK_ERR_LAUNCH;
-    }
-    configured = smem;
+  if (!grant_shared_memory(smem)) {
+    dk_set_error("gemm_tc: cannot get %zu bytes of shared memory", smem);
+    return DK_ERR_LAUNCH;
   }
   const int rows_out = swiglu ? 64 : TILE_ROWS;
   const int n_out = swiglu ? N / 2 : N;
@@ -418,15 +427,9 @@ extern "C" int dk_experts_gemm_tc(const void* x, const void* W, void* out, const
   CUtensorMap map_w, map_x;
   DK_REQUIRE(make_map(&map_w, W, (long long)E * a.expert_rows, K, K, glu ? 64 : TILE_ROWS), "experts_gemm_tc: cannot encode the tensor map of W");
   DK_REQUIRE(make_map(&map_x, x, M, K, K, a.mpad), "experts_gemm_tc: cannot encode the tensor map of x");
-  static size_t configured_on[DK_MAX_DEVICES] = {0};
-  size_t& configured = configured_on[dk_current_device()];
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) {
-      dk_set_error("experts_gemm_tc: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-      return DK_ERR_LAUNCH;
-    }
-    configured = smem;
+  if (!grant_shared_memory(smem)) {
+    dk_set_error("experts_gemm_tc: cannot get %zu bytes of shared memory", smem);
+    return DK_ERR_LAUNCH;
   }
   const int rows_out = glu ? 64 : TILE_ROWS;
   const int tiles = (n + rows_out - 1) / rows_out;
