@@ -164,6 +164,30 @@ def test_long_portions_run_their_chunks_in_parallel(tmp_path_factory, which, dty
     print("\nchunks in parallel worst", compare(res, refs, lengths, dtype, "long portions", noise))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions_at_the_edges_of_chunks(tmp_path_factory, dtype):
+    """Portions of exactly one and two chunks, one token more and one less, on both sides of the length from which the chunks run
+    in parallel; every request goes on with a portion that starts in the middle of a chunk and ends on a chunk's edge."""
+    from delta_b200.kernels import ops
+    from delta_b200.parts import decay_attention
+    c = ops.decay_attention_chunk()
+    assert decay_attention.PARALLEL_FROM == 2 * c + 1
+    cfg, W, folder = model(tmp_path_factory, "only_lightning")
+    first = [c, c + 1, 2 * c, 2 * c + 1, 3 * c - 1, 1]
+    lengths = [n + (4 * c - n) for n in first]           # every request ends at 4 chunks
+    toks = [helpers.random_tokens(n, cfg["vocab"], 500 + i) for i, n in enumerate(lengths)]
+    refs = [plain.forward(cfg, W, t)[0] for t in toks]
+    noise = rounding_noise(cfg, W, toks, refs) if dtype == "bfloat16" else None
+    for together in (True, False):      # the rows in one batch (the longest decides the path), and each alone (its own path)
+        runner = make_runner(folder, "only_lightning", dtype, max_batch=len(first))
+        if together:
+            steps = [[(i, 0, n) for i, n in enumerate(first)], [(i, n, lengths[i] - n) for i, n in enumerate(first)]]
+        else:
+            steps = [[(i, 0, n)] for i, n in enumerate(first)] + [[(i, n, lengths[i] - n)] for i, n in enumerate(first)]
+        res = helpers.run_schedule(runner, toks, steps)
+        compare(res, refs, lengths, dtype, f"chunk edges, together={together}", noise)
+
+
 def test_a_slot_used_again_starts_clean(tmp_path_factory):
     """Request B after request A in the same slot and pages equals B alone: state, previous token and cache of A are gone."""
     from delta_b200.engine.step import RowInput
