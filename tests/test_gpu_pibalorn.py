@@ -204,6 +204,40 @@ def test_a_slot_used_again_starts_clean(tmp_path_factory):
     assert err <= TOL["float32"] * ref.abs().max().item()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_far_key_carries_the_weight(tmp_path_factory, dtype):
+    """Weights made so that one score stands out: the key matrix is a permutation P and token B's embedding is P times token
+    A's, so the query of B (late in the prompt) meets the key of A (near its start, in the first page of many small ones) with
+    the largest score there is, and no other key comes close.  A kernel that misses that key, in a prompt portion or in a
+    single decoded token, changes the logits at B beyond any tolerance."""
+    d = 16
+    cfg = dict(architecture="Pibalorn", norm=dict(eps=1e-5), vocab=64, width=d, layers=[ph.bare(ph.attention(1, 1, d, 3.0))])
+    g = torch.Generator().manual_seed(77)
+    W = ph.make_weights(cfg, 9)
+    perm = torch.randperm(d, generator=g)
+    P = torch.eye(d)[perm]
+    W["embed"][1] = P @ W["embed"][0]
+    W["l0.mix.q"], W["l0.mix.k"], W["l0.mix.o"] = torch.eye(d), P.clone(), torch.eye(d) * 0.5
+    W["l0.norm1"] = torch.ones(d)
+    folder = ph.write_folder(tmp_path_factory.mktemp("far"), "far", cfg, W)
+    n, a_at, b_at = 150, 3, 140
+    toks = [2 + t % 62 for t in helpers.random_tokens(n, 62, 8)]
+    toks[a_at], toks[b_at] = 0, 1
+    ref = plain.forward(cfg, W, toks)[0]
+    without = list(toks)
+    without[a_at] = 5
+    changed = (plain.forward(cfg, W, without)[0][b_at] - ref[b_at]).abs().max().item()
+    assert changed > 0.2 * ref[b_at].abs().max().item(), "the crafted key does not carry the weight"
+    from delta_b200.config import EngineConfig
+    from delta_b200.engine.step import ModelRunner
+    runner = ModelRunner(folder, engine_config=EngineConfig(max_batch=2, max_seq_len=160, page_size=4, dtype=dtype, num_pages=80))
+    noise = rounding_noise(cfg, W, [toks], [ref]) if dtype == "bfloat16" else None
+    for what, steps in (("whole", [[(0, 0, n)]]), ("B decoded alone", [[(0, 0, b_at)]] + [[(0, p, 1)] for p in range(b_at, n)]),
+                        ("B opens a portion", [[(0, 0, 2)], [(0, 2, b_at - 2)], [(0, b_at, n - b_at)]]),
+                        ("B ends a portion", [[(0, 0, a_at)], [(0, a_at, 1)], [(0, a_at + 1, b_at - a_at)], [(0, b_at + 1, n - b_at - 1)]])):
+        compare(helpers.run_schedule(runner, [toks], steps), [ref], [n], dtype, what, noise)
+
+
 # ---- single kernels against their equations --------------------------------------------------------------------
 
 def _rows(lens, slots, dev):
